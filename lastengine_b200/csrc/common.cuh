@@ -1,0 +1,65 @@
+// Shared helpers of the sm_100a kernels: element types, warp reductions, error reporting.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and a stream, launches
+// asynchronously on that stream and returns 0, or returns non-zero after recording a message
+// that leb_last_error() hands out.  Nothing here allocates device memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define LEB_API extern "C" __attribute__((visibility("default")))
+
+// element type codes shared with the Python side
+enum LebDtype { LEB_F32 = 0, LEB_BF16 = 1 };
+
+int leb_fail(const char* fmt, ...);  // records the message, returns 1
+
+#define LEB_CHECK_LAUNCH(name)                                                        \
+  do {                                                                                \
+    cudaError_t e_ = cudaGetLastError();                                              \
+    if (e_ != cudaSuccess) return leb_fail("%s: %s", name, cudaGetErrorString(e_));   \
+  } while (0)
+
+#define LEB_REQUIRE(cond, ...)                 \
+  do {                                         \
+    if (!(cond)) return leb_fail(__VA_ARGS__); \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // `red` may still be read from an earlier call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

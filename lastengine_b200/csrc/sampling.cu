@@ -1,0 +1,196 @@
+// Next-token choice on the device, one block per sequence.
+//
+// The reference samples on the host (src/local.rs:59-80) in this order, kept here:
+//   penalties over the last 256 tokens, applied once per occurrence (repeat: l>0 ? l/rp : l*rp;
+//   presence: l -= pp) -> temperature <= 0: argmax -> the top_k largest logits (0 means 64, at
+//   most 256), sorted descending -> divide by temperature -> softmax with the maximum
+//   subtracted -> top-p: keep the shortest prefix whose cumulative probability reaches top_p
+//   (when 0 < top_p < 1) -> min-p: cut where p < p[0]*min_p, keeping at least one ->
+//   r = u * sum(kept); walk the kept list subtracting p until r <= 0.
+// The uniform number u comes from the caller (the reference's xorshift64 runs on the host).
+// Differences: equal logits are ordered by lower token id first (the reference's selection is
+// unstable, and its argmax returns the last of equal maxima).
+#include "common.cuh"
+
+#define SMP_THREADS 1024
+#define SMP_MAX_K 256
+
+__device__ __forceinline__ unsigned long long order_key(float v, int idx) {
+  unsigned u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // larger float -> larger unsigned
+  return ((unsigned long long)u << 32) | (unsigned)(0xffffffffu - (unsigned)idx);  // lower id wins
+}
+
+// one thread per sequence: occurrences compound in order, as in the reference's loop
+__global__ void penalties_rows_kernel(float* __restrict__ logits, const int* __restrict__ hist,
+                                      const int* __restrict__ hist_len, int hist_stride, int V,
+                                      int n, float repeat_penalty, float presence_penalty) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n) return;
+  float* l = logits + (size_t)b * V;
+  const int* h = hist + (size_t)b * hist_stride;
+  int len = hist_len[b];
+  for (int i = 0; i < len; i++) {
+    int t = h[i];
+    if (t < 0 || t >= V) continue;
+    float v = l[t];
+    if (repeat_penalty > 1.0f) v = v > 0.f ? v / repeat_penalty : v * repeat_penalty;
+    l[t] = v - presence_penalty;
+  }
+}
+
+LEB_API int leb_penalties(float* logits, const int* hist, const int* hist_len, int hist_stride,
+                          int n, int V, float repeat_penalty, float presence_penalty,
+                          cudaStream_t st) {
+  if (n <= 0) return 0;
+  penalties_rows_kernel<<<ceil_div(n, 64), 64, 0, st>>>(logits, hist, hist_len, hist_stride, V, n,
+                                                        repeat_penalty, presence_penalty);
+  LEB_CHECK_LAUNCH("leb_penalties");
+  return 0;
+}
+
+__global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
+  __shared__ unsigned long long best[32];
+  const float* l = logits + (size_t)blockIdx.x * V;
+  unsigned long long k = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    unsigned long long c = order_key(l[i], i);
+    k = c > k ? c : k;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long c = __shfl_xor_sync(0xffffffffu, k, o);
+    k = c > k ? c : k;
+  }
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) best[warp] = k;
+  __syncthreads();
+  if (warp == 0) {
+    k = lane < (int)(blockDim.x >> 5) ? best[lane] : 0ull;
+    for (int o = 16; o > 0; o >>= 1) {
+      unsigned long long c = __shfl_xor_sync(0xffffffffu, k, o);
+      k = c > k ? c : k;
+    }
+    if (lane == 0) out[blockIdx.x] = (int)(0xffffffffu - (unsigned)(k & 0xffffffffull));
+  }
+}
+
+LEB_API int leb_argmax(int* out, const float* logits, int n, int V, cudaStream_t st) {
+  if (n <= 0) return 0;
+  LEB_REQUIRE(V >= 1, "leb_argmax: empty vocabulary");
+  argmax_kernel<<<n, 512, 0, st>>>(out, logits, V);
+  LEB_CHECK_LAUNCH("leb_argmax");
+  return 0;
+}
+
+// Top-k by radix selection on the 64-bit (value, id) keys, a bitonic sort of the k winners, then
+// the reference's serial tail on one thread (at most 256 elements).
+__global__ void __launch_bounds__(SMP_THREADS)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ u01,
+              int V, int k, float temperature, float top_p, float min_p) {
+  __shared__ unsigned hist[256];
+  __shared__ unsigned long long prefix_s;
+  __shared__ int want_s;
+  __shared__ unsigned long long cand[SMP_MAX_K];
+  __shared__ float prob[SMP_MAX_K];
+  __shared__ int n_cand;
+  const float* l = logits + (size_t)blockIdx.x * V;
+  const int tid = threadIdx.x;
+
+  // k-th largest key: fix its bytes from the top
+  if (tid == 0) { prefix_s = 0ull; want_s = k; n_cand = 0; }
+  __syncthreads();
+  for (int byte = 7; byte >= 0; byte--) {
+    if (tid < 256) hist[tid] = 0u;
+    __syncthreads();
+    const unsigned long long prefix = prefix_s;
+    const unsigned long long himask = byte == 7 ? 0ull : (~0ull << (8 * (byte + 1)));
+    for (int i = tid; i < V; i += blockDim.x) {
+      unsigned long long key = order_key(l[i], i);
+      if ((key & himask) == prefix) atomicAdd(&hist[(unsigned)(key >> (8 * byte)) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int want = want_s;  // rank (from the top) of the wanted key among those matching the prefix
+      int b = 255;
+      for (; b > 0; b--) {
+        if ((int)hist[b] >= want) break;
+        want -= (int)hist[b];
+      }
+      prefix_s = prefix | ((unsigned long long)b << (8 * byte));
+      want_s = want;
+    }
+    __syncthreads();
+  }
+  const unsigned long long kth = prefix_s;  // keys are distinct: exactly k keys are >= kth
+  for (int i = tid; i < V; i += blockDim.x) {
+    unsigned long long key = order_key(l[i], i);
+    if (key >= kth) {
+      int p = atomicAdd(&n_cand, 1);
+      if (p < SMP_MAX_K) cand[p] = key;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < SMP_MAX_K; i += blockDim.x)
+    if (i >= k) cand[i] = 0ull;
+  __syncthreads();
+  // bitonic sort, descending, of SMP_MAX_K keys
+  for (int size = 2; size <= SMP_MAX_K; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (tid < SMP_MAX_K) {
+        int j = tid ^ stride;
+        if (j > tid) {
+          bool desc = (tid & size) == 0;
+          unsigned long long a = cand[tid], c = cand[j];
+          if (desc ? a < c : a > c) { cand[tid] = c; cand[j] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (tid == 0) {
+    auto logit_of = [&](int i) { return l[(int)(0xffffffffu - (unsigned)(cand[i] & 0xffffffffull))]; };
+    const float mx = logit_of(0) / temperature;
+    float z = 0.f;
+    for (int i = 0; i < k; i++) {
+      float p = expf(logit_of(i) / temperature - mx);
+      prob[i] = p;
+      z += p;
+    }
+    for (int i = 0; i < k; i++) prob[i] /= z;
+    int keep = k;
+    float cum = 0.f;
+    for (int i = 0; i < k; i++) {
+      cum += prob[i];
+      if (top_p > 0.f && top_p < 1.f && cum >= top_p) { keep = i + 1; break; }
+    }
+    if (min_p > 0.f) {
+      float thr = prob[0] * min_p;
+      int first_below = k;
+      for (int i = 0; i < k; i++)
+        if (prob[i] < thr) { first_below = i; break; }
+      keep = keep < first_below ? keep : first_below;
+      keep = keep < 1 ? 1 : keep;
+    }
+    float zk = 0.f;
+    for (int i = 0; i < keep; i++) zk += prob[i];
+    float r = u01[blockIdx.x] * zk;
+    int pick = keep - 1;
+    for (int i = 0; i < keep; i++) {
+      r -= prob[i];
+      if (r <= 0.f) { pick = i; break; }
+    }
+    out[blockIdx.x] = (int)(0xffffffffu - (unsigned)(cand[pick] & 0xffffffffull));
+  }
+}
+
+LEB_API int leb_sample(int* out, const float* logits, const float* u01, int n, int V, int top_k,
+                       float temperature, float top_p, float min_p, cudaStream_t st) {
+  if (n <= 0) return 0;
+  LEB_REQUIRE(temperature > 0.f, "leb_sample: temperature must be positive (use leb_argmax for greedy)");
+  int k = top_k == 0 ? 64 : (top_k < SMP_MAX_K ? top_k : SMP_MAX_K);  // src/local.rs:65
+  if (k > V) k = V;
+  LEB_REQUIRE(k >= 1, "leb_sample: empty vocabulary");
+  sample_kernel<<<n, SMP_THREADS, 0, st>>>(out, logits, u01, V, k, temperature, top_p, min_p);
+  LEB_CHECK_LAUNCH("leb_sample");
+  return 0;
+}

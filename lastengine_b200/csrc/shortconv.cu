@@ -1,0 +1,105 @@
+// Gated short convolution over packed rows of several sequences, with the state carried in
+// the cache between steps.
+//
+// For a token with projections (B, C, xg) = in_proj(h) split in this order
+// (src/dense.rs:156-161, src/cuda/dense.cu:126,131):
+//     bx_t = B_t * xg_t
+//     c_t  = sum_{j=0}^{Lc-1} w[ch, j] * bx_{t-(Lc-1)+j}      (w[ch, Lc-1] takes the current token,
+//                                                              src/dense.rs:163-164)
+//     y_t  = C_t * c_t  (+ bias[ch] inside c_t when the layer has one)
+// Values of bx before the first row of this step come from the state: the last Lc-1 values of
+// bx per channel, oldest first (src/dense.rs:165-166); a fresh sequence starts from zeros.
+// The reference runs the tokens of a chunk one after another per channel
+// (src/cuda/dense.cu:135-148); here every (row, channel) is independent because a tap reaches
+// back only Lc-1 rows, so the rows of a prompt are computed in parallel and a second kernel
+// writes the new state once all rows have read the old one.
+#include "common.cuh"
+
+template <typename T>
+__global__ void shortconv_rows_kernel(T* __restrict__ y, const T* __restrict__ bcx,
+                                      const float* __restrict__ w, const float* __restrict__ bias,
+                                      const float* __restrict__ state,
+                                      const int* __restrict__ row_seq,
+                                      const int* __restrict__ seq_slot,
+                                      const int* __restrict__ seq_qstart, int D, int Lc) {
+  int m = blockIdx.x;
+  int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  if (ch >= D) return;
+  int b = row_seq[m];
+  int slot = seq_slot[b];
+  T* yo = y + (size_t)m * D;
+  if (slot < 0) {  // padding row
+    yo[ch] = from_f32<T>(0.f);
+    return;
+  }
+  int i = m - seq_qstart[b];  // index of this row within its sequence's rows of this step
+  const float* wc = w + (size_t)ch * Lc;
+  const float* sc = state + ((size_t)slot * D + ch) * (Lc - 1);
+  float acc = bias ? bias[ch] : 0.f;
+  for (int j = 0; j < Lc; j++) {
+    int src = i - (Lc - 1) + j;  // row of this step, negative: before it
+    float bx;
+    if (src >= 0) {
+      const T* r = bcx + (size_t)(m - i + src) * 3 * D;
+      bx = to_f32(r[ch]) * to_f32(r[2 * D + ch]);
+    } else {
+      bx = sc[(Lc - 1) + src];
+    }
+    acc += wc[j] * bx;
+  }
+  const T* r = bcx + (size_t)m * 3 * D;
+  yo[ch] = from_f32<T>(to_f32(r[D + ch]) * acc);
+}
+
+// New state of each sequence: the last Lc-1 values of (old state ++ bx of this step's rows).
+template <typename T>
+__global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                       const int* __restrict__ seq_slot,
+                                       const int* __restrict__ seq_qstart,
+                                       const int* __restrict__ seq_qlen, int D, int Lc) {
+  int b = blockIdx.x;
+  int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  if (ch >= D) return;
+  int slot = seq_slot[b];
+  if (slot < 0) return;
+  int T_ = seq_qlen[b];
+  if (T_ <= 0) return;
+  int q0 = seq_qstart[b];
+  float* sc = state + ((size_t)slot * D + ch) * (Lc - 1);
+  float nv[16];
+  for (int k = 0; k < Lc - 1; k++) {
+    int src = T_ - (Lc - 1) + k;
+    if (src >= 0) {
+      const T* r = bcx + (size_t)(q0 + src) * 3 * D;
+      nv[k] = to_f32(r[ch]) * to_f32(r[2 * D + ch]);
+    } else {
+      nv[k] = sc[(Lc - 1) + src];
+    }
+  }
+  for (int k = 0; k < Lc - 1; k++) sc[k] = nv[k];
+}
+
+LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, const float* bias,
+                          float* state, const int* row_seq, const int* seq_slot,
+                          const int* seq_qstart, const int* seq_qlen, int M, int B, int D, int Lc,
+                          cudaStream_t st) {
+  if (M <= 0 || B <= 0) return 0;
+  LEB_REQUIRE(Lc >= 2 && Lc <= 17, "leb_shortconv: conv length %d outside 2..17", Lc);
+  dim3 block(128);
+  dim3 g1(M, ceil_div(D, 128)), g2(B, ceil_div(D, 128));
+  if (dtype == LEB_F32) {
+    shortconv_rows_kernel<float><<<g1, block, 0, st>>>((float*)y, (const float*)bcx, w, bias, state,
+                                                       row_seq, seq_slot, seq_qstart, D, Lc);
+    shortconv_state_kernel<float><<<g2, block, 0, st>>>((const float*)bcx, state, seq_slot,
+                                                        seq_qstart, seq_qlen, D, Lc);
+  } else if (dtype == LEB_BF16) {
+    shortconv_rows_kernel<bf16><<<g1, block, 0, st>>>((bf16*)y, (const bf16*)bcx, w, bias, state,
+                                                      row_seq, seq_slot, seq_qstart, D, Lc);
+    shortconv_state_kernel<bf16><<<g2, block, 0, st>>>((const bf16*)bcx, state, seq_slot,
+                                                       seq_qstart, seq_qlen, D, Lc);
+  } else {
+    return leb_fail("leb_shortconv: unknown dtype %d", dtype);
+  }
+  LEB_CHECK_LAUNCH("leb_shortconv");
+  return 0;
+}

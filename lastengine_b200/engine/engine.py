@@ -1,0 +1,179 @@
+"""The step function and what it stands on: model, cache, workspace.
+
+`Engine.step` takes a batch of sequences that either all start (their prompts, of unequal
+lengths, in one step) or all go on (one token each; any number of tokens each also works),
+runs exactly the tokens it is given as one packed batch against the cache, and returns the
+logits at the wanted rows.  The reference's counterpart serves one sequence: `prefill(ids)`
+gives the last position's logits and `forward(token)` the next (src/gpu/dense.rs:348,371).
+"""
+from __future__ import annotations
+
+import os
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache import Cache, CacheError
+from ..config.base import read_config_json
+from ..parts.base import BuildEnv, ModelPlan
+from ..registry import plan_from_config
+from .batch import BatchBuilder, StepBatch
+from .model import Model
+from .workspace import Workspace
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "f32": torch.float32}
+
+
+class StepError(ValueError):
+    """A step that cannot run: unknown sequence, empty token list, token id outside the vocabulary."""
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype {dtype} is not supported (bfloat16, float32)")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"unknown dtype '{dtype}' (bfloat16, float32)") from None
+
+
+class Engine:
+    def __init__(self, plan: ModelPlan, dtype="bfloat16", max_tokens: int = 8192,
+                 max_seqs: int | None = None, device: str | torch.device = "cuda:0"):
+        dev = torch.device(device)
+        if dev.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError("lastengine_b200 runs on a CUDA device only (no CPU path); "
+                               f"asked for '{device}', torch.cuda.is_available() = {torch.cuda.is_available()}")
+        torch.cuda.set_device(dev)
+        from ..ops import kernels
+        kernels.lib()   # build or load the kernels now: fail here, loudly, if they are missing
+        self.device = dev
+        self.dtype = resolve_dtype(dtype)
+        self.plan = plan
+        self.workspace = Workspace(dev)
+        self.env = BuildEnv(device=dev, dtype=self.dtype, workspace=self.workspace)
+        self.model = Model(plan, self.env)
+        self.max_tokens = int(max_tokens)
+        self.cache = Cache(self.model.cache_specs(), max_tokens=self.max_tokens, max_seqs=max_seqs,
+                           dtype=self.dtype, device=dev)
+        self.builder = BatchBuilder(dev)
+        self.vocab_size = plan.vocab_size
+        self.loaded = False
+
+    # ---- construction --------------------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
+        """A folder with config.json and model.safetensors; the model class is chosen by config.json."""
+        from ..weights import load_model_dir
+        raw = read_config_json(model_dir)
+        eng = cls(plan_from_config(raw), dtype=dtype, **kw)
+        load_model_dir(eng.model, model_dir)
+        eng.loaded = True
+        eng.config = raw
+        return eng
+
+    @classmethod
+    def from_config(cls, config: dict | str, seed: int = 0, dtype="bfloat16", norm_init: str = "ones",
+                    **kw) -> "Engine":
+        """Random weights made on the device from a configuration and a seed."""
+        from ..weights import load_random
+        raw = read_config_json(config) if isinstance(config, (str, os.PathLike)) else config
+        eng = cls(plan_from_config(raw), dtype=dtype, **kw)
+        load_random(eng.model, seed, norm_init=norm_init)
+        eng.loaded = True
+        eng.config = raw
+        return eng
+
+    # ---- sequences ------------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.alloc_seq()
+
+    def release(self, seqs: int | Sequence[int]) -> None:
+        for s in ([seqs] if isinstance(seqs, int) else seqs):
+            self.cache.free_seq(s)
+
+    def length(self, seq: int) -> int:
+        return self.cache.length(seq)
+
+    # ---- the step -------------------------------------------------------------------------
+    def prepare(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
+                want: str | Sequence[Sequence[int]] | None = "last",
+                u01: np.ndarray | None = None, builder: BatchBuilder | None = None,
+                table_width: int | None = None) -> tuple[StepBatch, dict[int, int]]:
+        """Checks a step, reserves its cache room and lays it out on the device."""
+        if not self.loaded:
+            raise RuntimeError("the engine has no weights yet")
+        if len(seqs) != len(tokens) or len(seqs) == 0:
+            raise StepError(f"a step needs as many token lists as sequences, and at least one "
+                            f"({len(seqs)} sequences, {len(tokens)} token lists)")
+        live = [s for s in seqs if s >= 0]
+        if len(set(live)) != len(live):
+            raise StepError("a sequence appears twice in one step")
+        V = self.vocab_size
+        pos0 = []
+        for s, t in zip(seqs, tokens):
+            if len(t) == 0:
+                raise StepError(f"sequence {s} brings no tokens to the step")
+            if s >= 0:
+                try:
+                    pos0.append(self.cache.length(s))
+                except CacheError:
+                    raise StepError(f"sequence {s} is not live (never started, or already released)") from None
+                ta = np.asarray(t)
+                if ta.min() < 0 or ta.max() >= V:
+                    bad = int(ta[(ta < 0) | (ta >= V)][0])
+                    raise StepError(f"token id {bad} of sequence {s} is outside the vocabulary [0, {V})")
+            else:
+                pos0.append(0)
+        if isinstance(want, str) and want == "last":
+            rows, r0 = [], 0
+            for t in tokens:
+                r0 += len(t)
+                rows.append(r0 - 1)
+        elif want is None:
+            rows = []
+        else:
+            if len(want) != len(seqs):
+                raise StepError("`want` needs one list of places per sequence")
+            rows, r0 = [], 0
+            for t, w in zip(tokens, want):
+                for i in w:
+                    if not 0 <= i < len(t):
+                        raise StepError(f"wanted place {i} is outside the {len(t)} tokens the sequence brings")
+                    rows.append(r0 + i)
+                r0 += len(t)
+        grow = {s: len(t) for s, t in zip(seqs, tokens) if s >= 0}
+        self.cache.reserve(grow)
+        tables = {}
+        for gi, g in enumerate(self.cache.kv_groups):
+            width = table_width or max(1, max((len(g.seq_pages.get(s, ())) for s in live), default=1))
+            tables[gi] = g.table(list(seqs), width)
+        b = (builder or self.builder).build(list(seqs), tokens, pos0, rows, tables, u01=u01)
+        return b, grow
+
+    def step(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: str | Sequence[Sequence[int]] | None = "last") -> torch.Tensor:
+        """Feeds `tokens[i]` to sequence `seqs[i]` and returns float logits [wanted rows, vocab].
+
+        `want`: "last" (the last token of each sequence), None (nothing), or per sequence the
+        places among its tokens of this step.  The result lives in workspace memory that the
+        next step overwrites: copy it if it must outlive the step.
+        """
+        batch, grow = self.prepare(seqs, tokens, want)
+        logits = self.model.forward(batch, self.cache)
+        self.cache.commit(grow)
+        return logits
+
+    # ---- numbers for reports --------------------------------------------------------------
+    def weight_bytes(self) -> int:
+        seen, n = set(), 0
+        for _, part in self.model.named_parts():
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor) and v.is_cuda and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    n += v.numel() * v.element_size()
+        return n

@@ -1,0 +1,368 @@
+"""Python face of the CUDA kernels: checks shapes and types, then calls the C entry points.
+
+Every function launches on torch's current stream and returns at once.  Tensors are only
+containers here: no torch arithmetic runs on the product path.  A call on a machine without
+the built library, or with tensors that are not on a CUDA device, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_void_p
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = _build.load()
+        _declare(_lib)
+    return _lib
+
+
+def _declare(L) -> None:
+    P, I, F, S = c_void_p, c_int, c_float, c_size_t
+    sig = {
+        "leb_embed": [P, P, I, P, I, I, I, P],
+        "leb_rmsnorm": [P, I, P, P, P, I, I, F, I, P],
+        "leb_swiglu": [P, I, P, I, I, I, P],
+        "leb_gather_rows": [P, P, I, P, I, I, I, P],
+        "leb_add": [P, P, S, P],
+        "leb_shortconv": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, P],
+        "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, P],
+        "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+        "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
+        "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
+        "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
+        "leb_moe_align": [P, P, P, P, I, I, P],
+        "leb_moe_combine": [P, P, P, P, I, I, I, I, P],
+        "leb_penalties": [P, P, P, I, I, I, F, F, P],
+        "leb_argmax": [P, P, I, I, P],
+        "leb_sample": [P, P, P, I, I, I, F, F, F, P],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = c_int
+    for name, args in _OPTIONAL.items():
+        fn = getattr(L, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = c_int
+
+
+# entry points that later files add; declared when present
+_OPTIONAL: dict[str, list] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib().leb_last_error().decode())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}, the kernels run on CUDA only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+
+
+def _dt(t: torch.Tensor, name: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"{name}: unsupported dtype {t.dtype}") from None
+
+
+# ----------------------------------------------------------------------------------------------
+def embed(x: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> None:
+    """x[m] = table[tokens[m]] as float."""
+    _cuda(x, "embed.x", torch.float32)
+    _cuda(table, "embed.table")
+    _cuda(tokens, "embed.tokens", torch.int32)
+    M, D = x.shape
+    V = table.shape[0]
+    assert table.shape[1] == D and tokens.numel() >= M
+    _check(lib().leb_embed(_ptr(x), _ptr(table), _dt(table, "embed.table"), _ptr(tokens), M, D, V, _stream()))
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
+            rows: torch.Tensor | None = None, add: bool = False) -> None:
+    """out = x * rsqrt(mean(x^2) + eps) * w  (out += ... when add).  x is float."""
+    _cuda(out, "rmsnorm.out")
+    _cuda(x, "rmsnorm.x", torch.float32)
+    _cuda(w, "rmsnorm.w", torch.float32)
+    M, D = out.shape
+    assert x.shape[1] == D and w.numel() == D
+    if rows is not None:
+        _cuda(rows, "rmsnorm.rows", torch.int32)
+        assert rows.numel() >= M
+    else:
+        assert x.shape[0] >= M
+    _check(lib().leb_rmsnorm(_ptr(out), _dt(out, "rmsnorm.out"), _ptr(x), _ptr(w), _ptr(rows), M, D,
+                             float(eps), 1 if add else 0, _stream()))
+
+
+def swiglu(out: torch.Tensor, gu: torch.Tensor) -> None:
+    """out[m, j] = silu(gu[m, j]) * gu[m, F + j]."""
+    _cuda(out, "swiglu.out")
+    _cuda(gu, "swiglu.gu")
+    M, Fd = out.shape
+    assert gu.shape == (M, 2 * Fd)
+    _check(lib().leb_swiglu(_ptr(out), _dt(out, "swiglu.out"), _ptr(gu), _dt(gu, "swiglu.gu"), M, Fd, _stream()))
+
+
+def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor, div: int = 1) -> None:
+    """out[p] = src[rows[p] // div]."""
+    _cuda(out, "gather_rows.out")
+    _cuda(src, "gather_rows.src", out.dtype)
+    _cuda(rows, "gather_rows.rows", torch.int32)
+    P_, D = out.shape
+    assert src.shape[1] == D and rows.numel() >= P_
+    _check(lib().leb_gather_rows(_ptr(out), _ptr(src), _dt(out, "gather_rows"), _ptr(rows), div, P_, D, _stream()))
+
+
+def add_(x: torch.Tensor, y: torch.Tensor) -> None:
+    _cuda(x, "add.x", torch.float32)
+    _cuda(y, "add.y", torch.float32)
+    assert x.numel() == y.numel()
+    _check(lib().leb_add(_ptr(x), _ptr(y), x.numel(), _stream()))
+
+
+def shortconv(y: torch.Tensor, bcx: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+              state: torch.Tensor, batch, Lc: int) -> None:
+    """Gated short convolution over the step's rows; updates `state` [slots, D, Lc-1] (float)."""
+    _cuda(y, "shortconv.y")
+    _cuda(bcx, "shortconv.bcx", y.dtype)
+    _cuda(w, "shortconv.w", torch.float32)
+    _cuda(state, "shortconv.state", torch.float32)
+    M, D = y.shape
+    assert bcx.shape == (M, 3 * D) and w.numel() == D * Lc
+    assert state.shape[1:] == (D, Lc - 1)
+    if bias is not None:
+        _cuda(bias, "shortconv.bias", torch.float32)
+    _check(lib().leb_shortconv(_ptr(y), _ptr(bcx), _dt(y, "shortconv"), _ptr(w), _ptr(bias), _ptr(state),
+                               _ptr(batch.row_seq), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
+                               _ptr(batch.seq_qlen), M, batch.n_seqs, D, Lc, _stream()))
+
+
+def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | None,
+                  v_in: torch.Tensor | None, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
+                  block_table: torch.Tensor, batch, q_norm_w, k_norm_w, eps: float,
+                  inv_freq: torch.Tensor | None, rope_dim: int, neox: bool, nh: int, nkv: int, hd: int,
+                  page_size: int) -> None:
+    """Per-head norm and rotation of q and k; k and v go to the paged cache, q to q_out.
+
+    q_in/k_in/v_in may be column slices of one fused projection (row stride = its width).
+    """
+    _cuda(q_out, "qk_rope_store.q_out")
+    _cuda(q_in, "qk_rope_store.q_in", q_out.dtype, contiguous=False)
+    M = q_out.shape[0]
+    assert q_in.stride(-1) == 1 and q_in.shape == (M, nh * hd)
+    q_stride = q_in.stride(0)
+    kv_stride = 0
+    if k_in is not None:
+        _cuda(k_in, "qk_rope_store.k_in", q_out.dtype, contiguous=False)
+        _cuda(v_in, "qk_rope_store.v_in", q_out.dtype, contiguous=False)
+        assert k_in.shape == (M, nkv * hd) and v_in.shape == (M, nkv * hd)
+        assert k_in.stride(0) == v_in.stride(0) and k_in.stride(-1) == 1 and v_in.stride(-1) == 1
+        kv_stride = k_in.stride(0)
+        _cuda(k_pool, "qk_rope_store.k_pool", q_out.dtype)
+        _cuda(v_pool, "qk_rope_store.v_pool", q_out.dtype)
+        assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape == k_pool.shape
+    _cuda(block_table, "qk_rope_store.block_table", torch.int32)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
+        if t is not None:
+            _cuda(t, f"qk_rope_store.{name}", torch.float32)
+    if inv_freq is not None:
+        assert inv_freq.numel() == rope_dim // 2
+    _check(lib().leb_qk_rope_store(
+        _ptr(q_out), _ptr(q_in), q_stride, _ptr(k_in), _ptr(v_in), kv_stride, _ptr(k_pool), _ptr(v_pool),
+        _dt(q_out, "qk_rope_store"), _ptr(block_table), block_table.shape[1], _ptr(batch.row_seq),
+        _ptr(batch.row_pos), _ptr(batch.seq_slot), _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
+        _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, _stream()))
+
+
+def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
+    """How many blocks share one sequence's key range in a decode step (1 for prompts)."""
+    if batch.max_qlen != 1:
+        return 1
+    per = batch.n_seqs * nkv * ((G + 7) // 8)
+    return max(1, min(16, (2 * sm_count) // max(per, 1)))
+
+
+def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+              block_table: torch.Tensor, batch, nh: int, nkv: int, hd: int, page_size: int,
+              window: int, scale: float, gate: torch.Tensor | None = None,
+              n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Causal attention of the step's rows over the paged cache (which already holds their keys)."""
+    _cuda(out, "attention.out")
+    _cuda(q, "attention.q", out.dtype)
+    _cuda(k_pool, "attention.k_pool", out.dtype)
+    _cuda(v_pool, "attention.v_pool", out.dtype)
+    _cuda(block_table, "attention.block_table", torch.int32)
+    M = out.shape[0]
+    assert out.shape == (M, nh * hd) and q.shape == (M, nh * hd)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape == k_pool.shape
+    gate_stride = 0
+    if gate is not None:
+        _cuda(gate, "attention.gate", out.dtype, contiguous=False)
+        assert gate.shape == (M, nh) and gate.stride(-1) == 1
+        gate_stride = gate.stride(0)
+    if n_splits > 1:
+        need = M * nh * n_splits * (hd + 2)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention: {n_splits} splits need {need} floats of scratch")
+        _cuda(scratch, "attention.scratch", torch.float32)
+    _check(lib().leb_attention(
+        _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention"),
+        _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
+        _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(gate), gate_stride, M, batch.n_seqs, nh, nkv,
+        hd, page_size, window, float(scale), batch.max_qlen, n_splits, _stream()))
+
+
+# ----------------------------------------------------------------------------------------------
+STORE, ACCUMULATE, SWIGLU = 0, 1, 2
+SMALL_M = 64  # rows up to which the weight-streaming kernel is used
+
+
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
+           group_offsets: torch.Tensor | None = None, rows_hint: int = 0) -> None:
+    """out (+)= x . w^T  with w [N, K] (or [E, N, K] with group_offsets [E+1] over the rows).
+
+    float32 operands run on the CUDA cores in true 32-bit; bfloat16 operands on the tensor
+    cores with float accumulation.  `epilogue`: STORE, ACCUMULATE (out is the float residual)
+    or SWIGLU (w holds gate and up rows interleaved in blocks of 16; out has N/2 columns).
+    """
+    _cuda(x, "linear.x", contiguous=False)
+    _cuda(w, "linear.w", x.dtype)
+    _cuda(out, "linear.out", contiguous=False)
+    M, K = x.shape
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    lda, ldc = x.stride(0), out.stride(0)
+    if group_offsets is not None:
+        _cuda(group_offsets, "linear.group_offsets", torch.int32)
+        E, N, Kw = w.shape
+        assert group_offsets.numel() == E + 1
+        stride = N * Kw
+    else:
+        N, Kw = w.shape
+        E, stride = 1, 0
+    assert Kw == K, f"linear: x has {K} columns, w has {Kw}"
+    n_out = N // 2 if epilogue == SWIGLU else N
+    assert out.shape == (M, n_out), f"linear: out is {tuple(out.shape)}, expected {(M, n_out)}"
+    if M == 0:
+        return
+    L = lib()
+    if x.dtype == torch.float32:
+        if epilogue == SWIGLU:
+            raise KernelError("linear: the float path keeps SwiGLU as its own kernel")
+        if out.dtype != torch.float32:
+            raise KernelError("linear: float operands need a float result")
+        _check(L.leb_gemm_f32(_ptr(out), _ptr(x), _ptr(w), M, N, K, lda, ldc, epilogue, _ptr(group_offsets),
+                              E, stride, _stream()))
+        return
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
+    hint = rows_hint if rows_hint > 0 else M
+    tc = _OPTIONAL_TC[0]
+    if tc is not None and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
+        return
+    _check(L.leb_gemm_bf16_small(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
+                                 epilogue, _ptr(group_offsets), E, stride, hint, _stream()))
+
+
+# set by ops.tc_gemm when the tensor-core (tcgen05) kernel is present
+_OPTIONAL_TC: list = [None]
+
+
+# ----------------------------------------------------------------------------------------------
+def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr: torch.Tensor,
+               bias: torch.Tensor | None, norm_topk: bool, scaling: float) -> None:
+    _cuda(topk_ids, "moe_router.topk_ids", torch.int32)
+    _cuda(topk_w, "moe_router.topk_w", torch.float32)
+    _cuda(h, "moe_router.h")
+    _cuda(wr, "moe_router.wr", torch.float32)
+    M, k = topk_ids.shape
+    E, D = wr.shape
+    assert h.shape == (M, D) and topk_w.shape == (M, k)
+    if bias is not None:
+        _cuda(bias, "moe_router.bias", torch.float32)
+        assert bias.numel() == E
+    _check(lib().leb_moe_router(_ptr(topk_ids), _ptr(topk_w), _ptr(h), _dt(h, "moe_router.h"), _ptr(wr),
+                                _ptr(bias), M, D, E, k, 1 if norm_topk else 0, float(scaling), _stream()))
+
+
+def moe_align(offsets: torch.Tensor, sorted_pair: torch.Tensor, pair_row: torch.Tensor,
+              topk_ids: torch.Tensor, E: int) -> None:
+    for n, t in (("offsets", offsets), ("sorted_pair", sorted_pair), ("pair_row", pair_row),
+                 ("topk_ids", topk_ids)):
+        _cuda(t, f"moe_align.{n}", torch.int32)
+    P_ = topk_ids.numel()
+    assert offsets.numel() >= E + 1 and sorted_pair.numel() >= P_ and pair_row.numel() >= P_
+    _check(lib().leb_moe_align(_ptr(offsets), _ptr(sorted_pair), _ptr(pair_row), _ptr(topk_ids), P_, E, _stream()))
+
+
+def moe_combine(x: torch.Tensor, ys: torch.Tensor, pair_row: torch.Tensor, topk_w: torch.Tensor,
+                accumulate: bool) -> None:
+    _cuda(x, "moe_combine.x", torch.float32)
+    _cuda(ys, "moe_combine.ys", torch.float32)
+    _cuda(pair_row, "moe_combine.pair_row", torch.int32)
+    _cuda(topk_w, "moe_combine.topk_w", torch.float32)
+    M, D = x.shape
+    k = topk_w.shape[1]
+    assert ys.shape[1] == D and ys.shape[0] >= M * k and topk_w.shape[0] == M
+    _check(lib().leb_moe_combine(_ptr(x), _ptr(ys), _ptr(pair_row), _ptr(topk_w), M, D, k,
+                                 1 if accumulate else 0, _stream()))
+
+
+# ----------------------------------------------------------------------------------------------
+def penalties(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Tensor,
+              repeat_penalty: float, presence_penalty: float) -> None:
+    _cuda(logits, "penalties.logits", torch.float32)
+    _cuda(hist, "penalties.hist", torch.int32)
+    _cuda(hist_len, "penalties.hist_len", torch.int32)
+    n, V = logits.shape
+    assert hist.shape[0] >= n
+    _check(lib().leb_penalties(_ptr(logits), _ptr(hist), _ptr(hist_len), hist.shape[1], n, V,
+                               float(repeat_penalty), float(presence_penalty), _stream()))
+
+
+def argmax(out: torch.Tensor, logits: torch.Tensor) -> None:
+    _cuda(out, "argmax.out", torch.int32)
+    _cuda(logits, "argmax.logits", torch.float32)
+    n, V = logits.shape
+    assert out.numel() >= n
+    _check(lib().leb_argmax(_ptr(out), _ptr(logits), n, V, _stream()))
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, u01: torch.Tensor, top_k: int, temperature: float,
+           top_p: float, min_p: float) -> None:
+    _cuda(out, "sample.out", torch.int32)
+    _cuda(logits, "sample.logits", torch.float32)
+    _cuda(u01, "sample.u01", torch.float32)
+    n, V = logits.shape
+    assert out.numel() >= n and u01.numel() >= n
+    _check(lib().leb_sample(_ptr(out), _ptr(logits), _ptr(u01), n, V, int(top_k), float(temperature),
+                            float(top_p), float(min_p), _stream()))

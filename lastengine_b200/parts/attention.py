@@ -1,0 +1,107 @@
+"""Grouped-query attention mixer over the paged cache.
+
+q = Wq h, k = Wk h, v = Wv h; optional per-head RMSNorm on q and k (shared [head_dim] weights,
+the model's eps) before the rotation; k and v appended to the cache at the token's position;
+causal softmax attention with scale 1/sqrt(head_dim), optionally inside a window; optional
+sigmoid gate per head from its own projection; out = Wo o.  (src/dense.rs:113-152.)
+The three projections (and the gate) are one matrix product over fused weights, as the
+reference fuses gate and up (src/gpu/dense.rs:67-74).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import kernels
+from ..registry import MIXERS, POSITION_ENCODINGS
+from .base import MATRIX, NORM, BuildEnv, KVSpec, Mixer, PartSpec, TensorSpec
+
+
+@MIXERS.register("attention")
+class AttentionMixer(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 norm_eps: float, qk_norm: bool = True, position: PartSpec | None = None,
+                 window: int = 0, output_gate: bool = False, own_kv: bool = True,
+                 scale: float | None = None):
+        if num_heads % num_kv_heads != 0:
+            raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} kv heads")
+        if head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is larger than the attention kernels take (256)")
+        self.D, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.eps = float(norm_eps)
+        self.qk_norm = bool(qk_norm)
+        self.window = int(window)
+        self.output_gate = bool(output_gate)
+        self.own_kv = bool(own_kv)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
+        pos = position or PartSpec("none")
+        self.position = POSITION_ENCODINGS.get(pos.kind)(**pos.params)
+        self.w_in = self.w_out = self.q_norm_w = self.k_norm_w = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        D, nh, nkv, hd = self.D, self.nh, self.nkv, self.hd
+        t = {"q_proj.weight": TensorSpec((nh * hd, D), MATRIX),
+             "out_proj.weight": TensorSpec((D, nh * hd), MATRIX)}
+        if self.own_kv:
+            t["k_proj.weight"] = TensorSpec((nkv * hd, D), MATRIX)
+            t["v_proj.weight"] = TensorSpec((nkv * hd, D), MATRIX)
+        if self.qk_norm:
+            t["q_layernorm.weight"] = TensorSpec((hd,), NORM)
+            if self.own_kv:
+                t["k_layernorm.weight"] = TensorSpec((hd,), NORM)
+        if self.output_gate:
+            t["gate_proj.weight"] = TensorSpec((nh, D), MATRIX)
+        return t
+
+    def cache_spec(self):
+        return KVSpec(self.nkv, self.hd, self.window)
+
+    def load(self, tensors, env: BuildEnv) -> None:
+        parts = [tensors["q_proj.weight"]]
+        if self.own_kv:
+            parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        if self.output_gate:
+            parts.append(tensors["gate_proj.weight"])
+        self.w_in = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
+        self.w_out = tensors["out_proj.weight"].contiguous()
+        if self.qk_norm:
+            self.q_norm_w = tensors["q_layernorm.weight"].contiguous()
+            self.k_norm_w = tensors["k_layernorm.weight"].contiguous() if self.own_kv else None
+        self.position.load({}, env)
+
+    def forward(self, h, out, accumulate, batch, cache, env) -> None:
+        nh, nkv, hd = self.nh, self.nkv, self.hd
+        M = h.shape[0]
+        ws = env.workspace
+        writes = self.own_kv and cache.writable
+        if self.own_kv and not cache.writable:
+            w_in = self.w_in[: nh * hd] if not self.output_gate else None
+        else:
+            w_in = self.w_in
+        if w_in is None:  # q and gate rows are not adjacent once k, v are skipped: two products
+            raise NotImplementedError("a gated attention layer reading another layer's cache")
+        proj = ws.get("attn.proj", (M, w_in.shape[0]), env.dtype)
+        kernels.linear(proj, h, w_in)
+        q_in = proj[:, : nh * hd]
+        k_in = v_in = gate = None
+        col = nh * hd
+        if writes:
+            k_in = proj[:, col: col + nkv * hd]
+            v_in = proj[:, col + nkv * hd: col + 2 * nkv * hd]
+            col += 2 * nkv * hd
+        if self.output_gate:
+            gate = proj[:, col: col + nh]
+        q = ws.get("attn.q", (M, nh * hd), env.dtype)
+        pe = self.position
+        kernels.qk_rope_store(q, q_in, k_in, v_in, cache.k if writes else None, cache.v if writes else None,
+                              cache.block_table, batch, self.q_norm_w, self.k_norm_w if writes else None,
+                              self.eps, pe.inv_freq, pe.rope_dim, pe.neox, nh, nkv, hd, cache.page_size)
+        o = ws.get("attn.o", (M, nh * hd), env.dtype)
+        n_splits = kernels.attention_splits(batch, nkv, nh // nkv)
+        scratch = None
+        if n_splits > 1:
+            scratch = ws.get("attn.part", (M * nh * n_splits * (hd + 2),), torch.float32)
+        kernels.attention(o, q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd, cache.page_size,
+                          self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch)
+        kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)

@@ -1,0 +1,158 @@
+"""What a part of a layer is, and what a model is made of.
+
+A layer is put together from parts: a mixer (attention, short convolution, ...), a
+feed-forward (dense or experts), norms and a position encoding, arranged by a block.
+Each part gets its sizes and constants as constructor arguments and knows nothing of the
+model around it.  Which parts a layer has is data (`PartSpec`), chosen layer by layer; the
+order in which layers run is data too (`ScheduleEntry`).
+
+Interfaces
+----------
+Every part:
+    tensors()  -> {relative name: TensorSpec}     what it reads from the checkpoint
+    load(tensors, env)                             takes its tensors (already on the device,
+                                                   in the dtype of their role) and may fuse them
+Mixer:
+    cache_spec() -> KVSpec | StateSpec | None      what it keeps per sequence
+    forward(h, out, accumulate, batch, cache, env) h: [rows, hidden] normed input in the
+                                                   activation dtype; writes (or adds) its
+                                                   result into the float tensor `out`
+FeedForward:
+    forward(h, out, accumulate, batch, env)
+Norm:
+    forward(out, x, rows=None, add=False)          x float; out in any activation dtype
+PositionEncoding:
+    table() -> float tensor the mixer's kernels use, and its constants as attributes
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+# roles decide the random initialisation and the dtype a tensor is kept in
+MATRIX = "matrix"        # operand of a matrix product: kept in the compute dtype
+EMBEDDING = "embedding"  # token table: compute dtype
+NORM = "norm"            # norm weight: kept float
+VECTOR = "vector"        # small per-channel parameters (conv taps, router rows): kept float
+BIAS = "bias"            # additive terms: kept float
+
+FLOAT_ROLES = (NORM, VECTOR, BIAS)
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    shape: tuple[int, ...]
+    role: str
+    std: float | None = None      # random init: normal(0, std); None: the model's default
+    optional: bool = False        # may be absent from the checkpoint
+
+
+@dataclass(frozen=True)
+class KVSpec:
+    """Keys and values that grow with the sequence; `window` > 0 keeps only the last ones."""
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """State of fixed size per sequence, zero when the sequence starts."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str                      # name in the registry of its family
+    params: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    prefix: str                    # tensor-name prefix of the layer, e.g. "layers.3"
+    mixer: PartSpec
+    ffn: PartSpec
+    mixer_norm: PartSpec
+    ffn_norm: PartSpec
+    post_mixer_norm: PartSpec | None = None
+    post_ffn_norm: PartSpec | None = None
+    block: str = "pre_norm_residual"
+    # tensor-name prefixes of the parts, relative to `prefix`
+    names: dict[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One step of the layer order: run `layer` with the cache entry `cache`.
+
+    By default entry i runs layer i with its own cache entry i.  Naming a layer twice runs
+    its weights twice; `cache` pointing at an earlier entry with `writes_cache=False` lets a
+    layer read what that entry stored instead of storing its own.
+    """
+    layer: int
+    cache: int | None = None
+    writes_cache: bool = True
+
+
+@dataclass
+class ModelPlan:
+    """Everything needed to build a model: parts, their order, and the tensor names."""
+    architecture: str
+    hidden_size: int
+    vocab_size: int
+    embedding: PartSpec
+    final_norm: PartSpec
+    head: PartSpec
+    layers: list[LayerSpec]
+    schedule: list[ScheduleEntry]
+    init_std: float = 0.02
+    eos_token_ids: tuple[int, ...] = ()
+    names: dict[str, str] = field(default_factory=dict)   # prefixes of embedding / final_norm / head
+    tensor_aliases: Any = None     # callable: checkpoint name -> canonical name (or None)
+
+    def __post_init__(self):
+        n = len(self.layers)
+        for i, e in enumerate(self.schedule):
+            if not 0 <= e.layer < n:
+                raise ValueError(f"schedule[{i}] names layer {e.layer}, the model has {n}")
+            c = i if e.cache is None else e.cache
+            if not 0 <= c < len(self.schedule):
+                raise ValueError(f"schedule[{i}] names cache entry {c}, outside the schedule")
+            if not e.writes_cache and c >= i:
+                raise ValueError(f"schedule[{i}] reads cache entry {c}, which has not run yet")
+
+
+@dataclass
+class BuildEnv:
+    """What parts need at build and run time besides their own parameters."""
+    device: torch.device
+    dtype: torch.dtype                 # activation / matrix dtype: float32 or bfloat16
+    workspace: Any = None              # engine.workspace.Workspace
+
+    @property
+    def is_float32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class Part:
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_spec(self) -> KVSpec | StateSpec | None:
+        return None
+
+    def forward(self, h, out, accumulate, batch, cache, env) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h, out, accumulate, batch, env) -> None:
+        raise NotImplementedError

@@ -1,0 +1,45 @@
+"""Gated short-convolution mixer.
+
+(B, C, x) = in_proj(h) split in this order; bx = B*x; causal depthwise convolution of length
+L over time with the last L-1 values of bx per channel carried as state; y = C * conv;
+out = out_proj(y).  No activation, no bias.  (src/dense.rs:153-170.)
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..registry import MIXERS
+from .base import MATRIX, VECTOR, BuildEnv, Mixer, StateSpec, TensorSpec
+
+
+@MIXERS.register("shortconv")
+class ShortConvMixer(Mixer):
+    def __init__(self, hidden_size: int, L_cache: int):
+        if not 2 <= L_cache <= 17:
+            raise ValueError(f"conv_L_cache {L_cache} outside what the kernel takes (2..17)")
+        self.D, self.Lc = int(hidden_size), int(L_cache)
+        self.w_in = self.w_conv = self.w_out = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        D, Lc = self.D, self.Lc
+        return {"in_proj.weight": TensorSpec((3 * D, D), MATRIX),
+                "conv.weight": TensorSpec((D, 1, Lc), VECTOR),
+                "out_proj.weight": TensorSpec((D, D), MATRIX)}
+
+    def cache_spec(self):
+        return StateSpec((self.D, self.Lc - 1), torch.float32)
+
+    def load(self, tensors, env: BuildEnv) -> None:
+        self.w_in = tensors["in_proj.weight"].contiguous()
+        self.w_conv = tensors["conv.weight"].reshape(self.D, self.Lc).contiguous()
+        self.w_out = tensors["out_proj.weight"].contiguous()
+
+    def forward(self, h, out, accumulate, batch, cache, env) -> None:
+        M = h.shape[0]
+        ws = env.workspace
+        bcx = ws.get("conv.bcx", (M, 3 * self.D), env.dtype)
+        kernels.linear(bcx, h, self.w_in)
+        y = ws.get("conv.y", (M, self.D), env.dtype)
+        kernels.shortconv(y, bcx, self.w_conv, None, cache.state, batch, self.Lc)
+        kernels.linear(out, y, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)
