@@ -1,0 +1,390 @@
+"""Each kernel alone against plain arithmetic, at sizes the tiny models do not use:
+widths and vocabularies that are no power of two, head sizes 16/48/80, odd group sizes,
+rows that are no multiple of any tile."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import harness as H  # noqa: F401  (path setup)
+import plain_lfm3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def K():
+    from lastengine_b200.ops import kernels
+    return kernels
+
+
+def builder():
+    from lastengine_b200.engine.batch import BatchBuilder
+    return BatchBuilder(torch.device(DEV))
+
+
+def gen(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(*shape, generator=g)).to(dtype)
+
+
+def err(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / (want.abs().max() + 1e-30))
+
+
+# ---- rows ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = gen(301, 72, seed=1).to(dtype)
+    toks = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    x = torch.empty(5, 72, device=DEV)
+    K().embed(x, table.to(DEV), toks.to(DEV))
+    assert torch.equal(x.cpu(), table.float()[toks.long()])
+
+
+@pytest.mark.parametrize("D", [100, 64, 2048, 5000])
+def test_rmsnorm(D):
+    x, w = gen(7, D, seed=2, scale=3.0), 1 + 0.1 * gen(D, seed=3)
+    want = P.rms_norm(x.double(), w.double(), 1e-3)
+    out = torch.empty(7, D, device=DEV)
+    K().rmsnorm(out, x.to(DEV), w.to(DEV), 1e-3)
+    assert err(out, want) < 1e-6
+    ob = torch.empty(7, D, device=DEV, dtype=torch.bfloat16)
+    K().rmsnorm(ob, x.to(DEV), w.to(DEV), 1e-3)
+    assert torch.equal(ob.cpu(), out.cpu().to(torch.bfloat16))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    o3 = torch.empty(3, D, device=DEV)
+    K().rmsnorm(o3, x.to(DEV), w.to(DEV), 1e-3, rows=rows)
+    assert torch.equal(o3.cpu(), out.cpu()[[6, 0, 3]])
+    res = gen(7, D, seed=4).to(DEV)
+    r0 = res.clone()
+    K().rmsnorm(res, x.to(DEV), w.to(DEV), 1e-3, add=True)
+    assert err(res, r0.cpu().double() + want) < 1e-6
+
+
+def test_swiglu():
+    gu = gen(9, 2 * 37, seed=5, scale=2.0)
+    want = P.silu(gu[:, :37].double()) * gu[:, 37:].double()
+    out = torch.empty(9, 37, device=DEV)
+    K().swiglu(out, gu.to(DEV))
+    assert err(out, want) < 1e-6
+    ob = torch.empty(9, 37, device=DEV, dtype=torch.bfloat16)
+    K().swiglu(ob, gu.to(DEV))
+    assert err(ob, want) < 5e-3
+
+
+# ---- matrix products ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(1, 50, 70), (37, 129, 33), (64, 64, 16), (130, 70, 200)])
+def test_linear_f32(M, N, K_):
+    x, w = gen(M, K_, seed=6), gen(N, K_, seed=7)
+    want = x.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV))
+    assert err(out, want) < 2e-6
+    base = gen(M, N, seed=8).to(DEV)
+    b0 = base.clone()
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert err(base, b0.cpu().double() + want) < 2e-6
+    # a row's result does not depend on the other rows of the launch
+    one = torch.empty(1, N, device=DEV)
+    K().linear(one, x[M - 1:].to(DEV), w.to(DEV))
+    assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 33, 64, 65, 200])
+@pytest.mark.parametrize("N,K_", [(48, 72), (100, 200), (17, 40)])
+def test_linear_bf16_small(M, N, K_):
+    x, w = gen(M, K_, seed=9, dtype=torch.bfloat16), gen(N, K_, seed=10, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV))
+    assert err(out, want) < 1e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=11).to(DEV)
+    b0 = base.clone()
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert err(base, b0.cpu().double() + want) < 1e-5
+    one = torch.empty(1, N, device=DEV)
+    K().linear(one, x[M - 1:].to(DEV), w.to(DEV))
+    assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
+
+
+@pytest.mark.parametrize("M,F,D", [(3, 48, 72), (40, 160, 96), (70, 16, 40)])
+def test_linear_bf16_swiglu_epilogue(M, F, D):
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    x = gen(M, D, seed=12, dtype=torch.bfloat16)
+    w1, w3 = gen(F, D, seed=13, dtype=torch.bfloat16), gen(F, D, seed=14, dtype=torch.bfloat16)
+    want = P.silu(x.double() @ w1.double().T) * (x.double() @ w3.double().T)
+    w13 = fuse_gate_up(w1, w3, True).to(DEV)
+    out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    K().linear(out, x.to(DEV), w13, K().SWIGLU)
+    assert err(out, want) < 6e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_grouped(dtype):
+    E, N, K_ = 5, 40, 56
+    counts = [3, 0, 70, 1, 9]
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
+    Ptot = int(offs[-1])
+    x, w = gen(Ptot, K_, seed=15, dtype=dtype), gen(E, N, K_, seed=16, dtype=dtype)
+    want = torch.zeros(Ptot, N, dtype=torch.float64)
+    for e in range(E):
+        a, b = int(offs[e]), int(offs[e + 1])
+        want[a:b] = x[a:b].double() @ w[e].double().T
+    out = torch.empty(Ptot, N, device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV), rows_hint=Ptot)
+    assert err(out, want) < 1e-5
+
+
+# ---- short convolution ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Lc,D", [(3, 72), (4, 130), (2, 64)])
+def test_shortconv_with_state(dtype, Lc, D):
+    """Three sequences with unequal rows in two consecutive steps, one of them shorter than the
+    convolution reaches back; compared with the plain convolution over the joined rows."""
+    lens1, lens2 = [1, 5, 2], [3, 1, 1]
+    slots = [4, 0, 2]
+    w = gen(D, Lc, seed=17)
+    bcx_all = [gen(a + b, 3 * D, seed=20 + i, dtype=dtype) for i, (a, b) in enumerate(zip(lens1, lens2))]
+    state = torch.full((6, D, Lc - 1), 7.0, device=DEV)   # stale contents of other slots
+    for s in slots:
+        state[s].zero_()
+    bb = builder()
+    got = [[] for _ in slots]
+    for step, lens in enumerate((lens1, lens2)):
+        lo = [0] * 3 if step == 0 else lens1
+        rows = torch.cat([bcx_all[i][lo[i]:lo[i] + lens[i]] for i in range(3)]).to(DEV)
+        batch = bb.build(slots, [[0] * n for n in lens], lo, [], {})
+        y = torch.empty(sum(lens), D, device=DEV, dtype=dtype)
+        K().shortconv(y, rows, w.to(DEV), None, state, batch, Lc)
+        r0 = 0
+        for i, n in enumerate(lens):
+            got[i].append(y[r0:r0 + n].float().cpu())
+            r0 += n
+    for i in range(3):
+        bcx = bcx_all[i].double()
+        bx = bcx[:, :D] * bcx[:, 2 * D:]
+        padded = torch.cat([torch.zeros(Lc - 1, D, dtype=torch.float64), bx])
+        acc = sum(padded[j:j + bx.shape[0]] * w.double()[:, j][None] for j in range(Lc))
+        want = bcx[:, D:2 * D] * acc
+        assert err(torch.cat(got[i]), want) < (1e-6 if dtype == torch.float32 else 5e-3)
+        assert err(state[slots[i]].cpu().T, padded[-(Lc - 1):]) < 1e-6      # oldest first
+    assert float(state[1].min()) == 7.0 and float(state[5].max()) == 7.0     # other slots untouched
+
+
+# ---- rotation and cache write ---------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rope_dim", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80)])
+def test_qk_rope_store(dtype, nh, nkv, hd, rope_dim):
+    page = 64
+    lens, pos0 = [3, 70], [62, 5]                   # rows cross a page boundary
+    M = sum(lens)
+    width = nh * hd + 2 * nkv * hd
+    qkv = gen(M, width, seed=30, dtype=dtype)
+    qn, kn = 1 + 0.1 * gen(hd, seed=31), 1 + 0.1 * gen(hd, seed=32)
+    theta, eps = 12345.0, 1e-4
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rope_dim // 2, dtype=torch.float64) / rope_dim).float()
+    n_pages = 8
+    tables = {0: np.array([[5, 2, -1], [1, 7, 3]], dtype=np.int32)}
+    kp = torch.zeros(n_pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    batch = builder().build([0, 1], [[0] * n for n in lens], pos0, [], tables)
+    q_out = torch.empty(M, nh * hd, device=DEV, dtype=dtype)
+    qd = qkv.to(DEV)
+    K().qk_rope_store(q_out, qd[:, :nh * hd], qd[:, nh * hd:(nh + nkv) * hd], qd[:, (nh + nkv) * hd:], kp, vp,
+                      batch.tables[0], batch, qn.to(DEV), kn.to(DEV), eps, inv.to(DEV), rope_dim, True, nh, nkv, hd, page)
+    tol = 1e-5 if dtype == torch.float32 else 6e-3
+    r0 = 0
+    for b, n in enumerate(lens):
+        rows = qkv[r0:r0 + n].double()
+        pos = torch.arange(pos0[b], pos0[b] + n)
+        q = P.rope(P.rms_norm(rows[:, :nh * hd].view(n, nh, hd), qn.double(), eps), pos, rope_dim, theta)
+        k = P.rope(P.rms_norm(rows[:, nh * hd:(nh + nkv) * hd].view(n, nkv, hd), kn.double(), eps), pos, rope_dim, theta)
+        v = rows[:, (nh + nkv) * hd:].view(n, nkv, hd)
+        assert err(q_out[r0:r0 + n].view(n, nh, hd), q) < tol
+        for i, p_ in enumerate(pos.tolist()):
+            pg = int(tables[0][b, p_ // page])
+            assert err(kp[pg, :, p_ % page, :], k[i]) < tol
+            assert err(vp[pg, :, p_ % page, :], v[i]) < tol
+        r0 += n
+
+
+# ---- attention ---------------------------------------------------------------------------------------
+def plain_attention(q, k, v, qpos, window, scale):
+    """q [Tq, nh, hd], k/v [Tk, nkv, hd] (positions 0..Tk-1), qpos [Tq]."""
+    Tq, nh, hd = q.shape
+    nkv = k.shape[1]
+    out = torch.zeros_like(q)
+    t = torch.arange(k.shape[0])
+    for h in range(nh):
+        s = (q[:, h] @ k[:, h // (nh // nkv)].T) * scale
+        ok = t[None] <= qpos[:, None]
+        if window > 0:
+            ok &= t[None] > qpos[:, None] - window
+        s = s.masked_fill(~ok, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // (nh // nkv)]
+    return out
+
+
+def fill_cache(k, v, pages, nkv, hd, page, dtype):
+    n_pages = max(pages) + 2
+    kp = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)   # unused places hold NaN
+    vp = torch.full_like(kp, float("nan"))
+    for t in range(k.shape[0]):
+        kp[pages[t // page], :, t % page] = k[t].to(dtype)
+        vp[pages[t // page], :, t % page] = v[t].to(dtype)
+    return kp.to(DEV), vp.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 48), (10, 5, 80), (16, 1, 32), (8, 8, 128)])
+@pytest.mark.parametrize("window", [0, 40])
+def test_attention_prompt_and_decode(dtype, nh, nkv, hd, window):
+    page, Tk = 64, 150
+    k, v = gen(Tk, nkv, hd, seed=40, dtype=dtype), gen(Tk, nkv, hd, seed=41, dtype=dtype)
+    pages = [3, 0, 5]
+    kp, vp = fill_cache(k, v, pages, nkv, hd, page, dtype)
+    scale = 1 / math.sqrt(hd)
+    tol = 2e-5 if dtype == torch.float32 else 8e-3
+    tables = {0: np.array([pages], dtype=np.int32)}
+    # a chunk of 37 rows continuing at position 100, then a single row at the end, split four ways
+    for q0, n, splits in ((100, 37, 1), (0, 150, 1), (149, 1, 1), (149, 1, 4), (70, 1, 16)):
+        q = gen(n, nh, hd, seed=42 + n, dtype=dtype)
+        batch = builder().build([0], [[0] * n], [q0], [], tables)
+        out = torch.empty(n, nh * hd, device=DEV, dtype=dtype)
+        scratch = torch.empty(n * nh * splits * (hd + 2), device=DEV) if splits > 1 else None
+        K().attention(out, q.reshape(n, nh * hd).to(DEV), kp, vp, batch.tables[0], batch, nh, nkv, hd, page,
+                      window, scale, n_splits=splits, scratch=scratch)
+        want = plain_attention(q.double(), k.double(), v.double(), torch.arange(q0, q0 + n), window, scale)
+        assert err(out.view(n, nh, hd), want) < tol, (q0, n, splits)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_far_key_and_window_edge(dtype):
+    """One early key is made to dominate: among hundreds of keys the output must be its value;
+    with a window that ends just before it, it must vanish, and one position earlier it must not."""
+    nh, nkv, hd, page, Tk = 4, 2, 64, 64, 300
+    k, v = gen(Tk, nkv, hd, seed=50, scale=0.1), gen(Tk, nkv, hd, seed=51)
+    q = gen(1, nh, hd, seed=52, scale=0.1)
+    far = 3
+    k[far] = 0
+    k[far, :, 0] = 40.0
+    q[..., 0] = 40.0                       # score 1600/8 = 200 against O(1) elsewhere
+    k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+    pages = [1, 4, 2, 0, 6]
+    kp, vp = fill_cache(k, v, pages, nkv, hd, page, dtype)
+    tables = {0: np.array([pages], dtype=np.int32)}
+    scale = 1 / math.sqrt(hd)
+    for splits in (1, 5):
+        for window, sees in ((0, True), (Tk - far, True), (Tk - far - 1, False)):
+            batch = builder().build([0], [[0]], [Tk - 1], [], tables)
+            out = torch.empty(1, nh * hd, device=DEV, dtype=dtype)
+            scratch = torch.empty(nh * splits * (hd + 2), device=DEV)
+            K().attention(out, q.reshape(1, nh * hd).to(DEV), kp, vp, batch.tables[0], batch, nh, nkv, hd, page,
+                          window, scale, n_splits=splits, scratch=scratch)
+            want = plain_attention(q.double(), k.double(), v.double(), torch.tensor([Tk - 1]), window, scale)
+            assert err(out.view(1, nh, hd), want) < (2e-5 if dtype == torch.float32 else 8e-3)
+            hit = err(out.view(1, nh, hd)[0, 0], v[far, 0].double()) < 1e-2
+            assert hit == sees, (splits, window)
+
+
+def test_attention_batch_of_unequal_sequences():
+    """Several sequences in one launch, each with its own pages, lengths and row counts; one is padding."""
+    dtype, nh, nkv, hd, page = torch.float32, 6, 2, 48, 64
+    lens_k, pos0, qn = [90, 10, 130], [60, 0, 129], [30, 10, 1]
+    ks = [gen(n, nkv, hd, seed=60 + i) for i, n in enumerate(lens_k)]
+    vs = [gen(n, nkv, hd, seed=70 + i) for i, n in enumerate(lens_k)]
+    pools_k = torch.full((12, nkv, page, hd), float("nan"))
+    pools_v = torch.full_like(pools_k, float("nan"))
+    page_lists = [[7, 2], [9], [0, 11, 4]]
+    for i in range(3):
+        for t in range(lens_k[i]):
+            pools_k[page_lists[i][t // page], :, t % page] = ks[i][t]
+            pools_v[page_lists[i][t // page], :, t % page] = vs[i][t]
+    table = np.full((4, 3), -1, dtype=np.int32)
+    for i, pl in enumerate(page_lists):
+        table[i if i < 2 else 3, :len(pl)] = pl
+    slots, rows = [0, 1, -1, 2], [qn[0], qn[1], 2, qn[2]]
+    qs = [gen(n, nh, hd, seed=80 + i) for i, n in enumerate(rows)]
+    batch = builder().build(slots, [[0] * n for n in rows], [pos0[0], pos0[1], 0, pos0[2]], [], {0: table})
+    M = sum(rows)
+    out = torch.empty(M, nh * hd, device=DEV)
+    K().attention(out, torch.cat(qs).reshape(M, nh * hd).to(DEV), pools_k.to(DEV), pools_v.to(DEV), batch.tables[0],
+                  batch, nh, nkv, hd, page, 0, 0.2)
+    r0 = 0
+    for j, (s, n) in enumerate(zip(slots, rows)):
+        if s >= 0:
+            p0 = [pos0[0], pos0[1], 0, pos0[2]][j]
+            want = plain_attention(qs[j].double(), ks[s].double(), vs[s].double(), torch.arange(p0, p0 + n), 0, 0.2)
+            assert err(out[r0:r0 + n].view(n, nh, hd), want) < 2e-5
+        else:
+            assert float(out[r0:r0 + n].abs().max()) == 0.0
+        r0 += n
+
+
+# ---- experts ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,k,norm,bias,scaling", [(8, 2, True, True, 1.0), (5, 1, False, False, 1.5), (32, 4, True, True, 2.0)])
+def test_moe_router_align_combine(dtype, E, k, norm, bias, scaling):
+    M, D = 77, 104
+    h = gen(M, D, seed=90, dtype=dtype)
+    wr, b = gen(E, D, seed=91, scale=0.3), gen(E, seed=92, scale=0.1)
+    ids_w, wts_w, _ = P.moe_route(h.double(), wr.double(), b.double() if bias else None, k, norm, scaling)
+    ids = torch.empty(M, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(M, k, device=DEV)
+    K().moe_router(ids, wts, h.to(DEV), wr.to(DEV), b.to(DEV) if bias else None, norm, scaling)
+    assert torch.equal(ids.cpu().long(), ids_w)
+    assert err(wts, wts_w) < 1e-5
+    offs = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    sp = torch.empty(M * k, dtype=torch.int32, device=DEV)
+    pr = torch.empty(M * k, dtype=torch.int32, device=DEV)
+    K().moe_align(offs, sp, pr, ids, E)
+    flat = ids_w.reshape(-1)
+    order = torch.sort(flat, stable=True).indices              # stable in the pair index
+    assert torch.equal(sp.cpu().long(), order)
+    assert torch.equal(offs.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), torch.bincount(flat, minlength=E).cumsum(0)]))
+    assert torch.equal(pr.cpu().long()[order], torch.arange(M * k))
+    ys = gen(M * k, D, seed=93)
+    x = gen(M, D, seed=94).to(DEV)
+    x0 = x.cpu().double()
+    K().moe_combine(x, ys.to(DEV), pr, wts, True)
+    want = x0 + (wts_w[:, :, None] * ys.double()[pr.cpu().long().view(M, k)]).sum(1)
+    assert err(x, want) < 1e-5
+
+
+# ---- sampling ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [256, 1000, 65536])
+def test_argmax_and_sampling(V):
+    n = 6
+    logits = gen(n, V, seed=95, scale=3.0)
+    logits[2, 17] = logits[2, 400 % V] = logits[2].max() + 1       # a tie: the lower id wins
+    ld = logits.to(DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    K().argmax(out, ld)
+    assert out.cpu().tolist() == [int(np.argmax(r)) for r in logits.numpy()]
+    for temperature, top_k, top_p, min_p in ((0.8, 40, 0.95, 0.0), (1.3, 0, 1.0, 0.05), (0.5, 500, 0.5, 0.0), (1.0, 1, 0.0, 0.0)):
+        for trial in range(4):
+            u = np.random.default_rng(trial).random(n).astype(np.float32)
+            K().sample(out, ld, torch.from_numpy(u).to(DEV), top_k, temperature, top_p, min_p)
+            want = [P.sample(logits[i].numpy(), temperature, top_k, top_p, min_p, float(u[i])) for i in range(n)]
+            assert out.cpu().tolist() == want, (temperature, top_k, top_p, min_p, trial)
+
+
+def test_penalties():
+    V = 50
+    logits = gen(2, V, seed=96)
+    hist = torch.zeros(2, 256, dtype=torch.int32)
+    hist[0, :4] = torch.tensor([3, 7, 3, 9])
+    ln = torch.tensor([4, 0], dtype=torch.int32)
+    want = logits.clone()
+    for t in [3, 7, 3, 9]:
+        v = want[0, t]
+        want[0, t] = (v / 1.3 if v > 0 else v * 1.3) - 0.2
+    ld = logits.to(DEV)
+    K().penalties(ld, hist.to(DEV), ln.to(DEV), 1.3, 0.2)
+    assert err(ld, want) < 1e-6
