@@ -50,6 +50,39 @@ def plain_logits(cfg: dict, model_dir: str, tokens, bf16: bool) -> torch.Tensor:
     return P.forward(cfg, t, tokens, rnd=P.round_bf16 if bf16 else P.identity)
 
 
+# A router near-tie is a discontinuity: when the chosen and the first rejected expert score
+# closer than bfloat16 rounding moves them, rounding decides which expert runs, and the logits
+# of that position jump.  Such positions (found by the plain implementation alone) are left
+# out of bfloat16 comparisons; in 32-bit every position is compared.
+ROUTER_GAP_BF16 = 1e-3
+ROUTER_GAP_F32 = 1e-5
+
+
+def plain_logits_and_margins(cfg: dict, model_dir: str, tokens, bf16: bool):
+    """Plain logits [T, V] and, per position, the smallest gap between the last chosen and the
+    first rejected expert score over the model's routed layers (inf without experts)."""
+    margins = []
+    orig = P.moe_route
+
+    def spy(h, wr, bias, k, norm_topk, scaling):
+        ids, w, c = orig(h, wr, bias, k, norm_topk, scaling)
+        cs = torch.sort(c, dim=-1, descending=True).values
+        margins.append(cs[:, k - 1] - cs[:, k] if cs.shape[1] > k else torch.full((cs.shape[0],), float("inf")))
+        return ids, w, c
+    P.moe_route = spy
+    try:
+        lg = plain_logits(cfg, model_dir, tokens, bf16)
+    finally:
+        P.moe_route = orig
+    m = torch.stack(margins).amin(0) if margins else torch.full((len(tokens),), float("inf"), dtype=torch.float64)
+    return lg, m
+
+
+def decided(margins: torch.Tensor, bf16: bool) -> torch.Tensor:
+    """Positions whose routing does not hang on rounding."""
+    return margins > (ROUTER_GAP_BF16 if bf16 else ROUTER_GAP_F32)
+
+
 def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     got, want = got.double().cpu(), want.double().cpu()
     return float((got - want).abs().max() / want.abs().max())

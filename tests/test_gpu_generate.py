@@ -21,14 +21,15 @@ def dirs(tmp_path_factory):
             "B": H.make_model_dir(TINY_B, 1, str(tmp_path_factory.mktemp("genB")))}
 
 
-def plain_greedy(cfg, tensors, prompt, n, rnd):
+def plain_greedy(cfg, model_dir, prompt, n, bf16):
     """Greedy continuation by the plain implementation, with the margin between the two best
-    logits at every step."""
+    logits at every step (0 where the step's routing hangs on rounding)."""
     toks, out, margins = list(prompt), [], []
     for _ in range(n):
-        lg = P.forward(cfg, tensors, toks, rnd=rnd)[-1]
+        lg, rm = H.plain_logits_and_margins(cfg, model_dir, toks, bf16)
+        lg = lg[-1]
         top = torch.topk(lg, 2).values
-        margins.append(float((top[0] - top[1]) / lg.abs().max()))
+        margins.append(float((top[0] - top[1]) / lg.abs().max()) if H.decided(rm, bf16)[-1] else 0.0)
         t = int(torch.argmax(lg))
         out.append(t)
         toks.append(t)
@@ -36,23 +37,22 @@ def plain_greedy(cfg, tensors, prompt, n, rnd):
 
 
 @pytest.mark.parametrize("name,cfg,lens,steps", [("A", TINY_A, [5, 11, 17], 8), ("B", TINY_B, [1, 7, 23, 40], 12)])
-@pytest.mark.parametrize("dtype,rnd,gap", [("float32", P.identity, 1e-4), ("bfloat16", P.round_bf16, 3e-2)])
-def test_greedy_generation_matches_plain(name, cfg, lens, steps, dtype, rnd, gap, dirs):
+@pytest.mark.parametrize("dtype,bf16,gap", [("float32", False, H.TOL_F32), ("bfloat16", True, H.TOL_BF16)])
+def test_greedy_generation_matches_plain(name, cfg, lens, steps, dtype, bf16, gap, dirs):
     from lastengine_b200 import Engine, SamplingParams
     eng = Engine.from_pretrained(dirs[name], dtype=dtype, max_tokens=1024)
     prompts = H.requests_for(cfg, lens, 21)
     res = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=steps, stop_token_ids=[])
-    tensors = P.read_safetensors(os.path.join(dirs[name], "model.safetensors"), torch.float64)
     compared = 0
     for p, got, reason in zip(prompts, res.tokens, res.finish_reasons):
-        want, margins = plain_greedy(cfg, tensors, p, steps, rnd)
+        want, margins = plain_greedy(cfg, dirs[name], p, steps, bf16)
         assert len(got) == steps and reason == "length"
         for i in range(steps):
-            if margins[i] < gap:        # the two best logits are closer than the path's rounding: stop here
+            if margins[i] < gap:        # the two best logits are closer than the path's tolerance: stop here
                 break
             assert got[i] == want[i], f"{name} {dtype}: prompt of {len(p)}, token {i}: {got[i]} != {want[i]}"
             compared += 1
-    assert compared >= steps * len(prompts) // 2
+    assert compared >= steps * len(prompts) // 3
     assert eng.cache.slots.n_held == 0
     eng.cache.check()
 
@@ -137,10 +137,14 @@ def test_trace_run_program(dtype, bf16, tol, dirs, tmp_path):
     run_trace(dirs["B"], dtype, steps, out, max_tokens=256)
     assert not os.path.exists(os.path.join(out, "1.f32"))
     V = cfg["vocab_size"]
-    tensors = P.read_safetensors(os.path.join(dirs["B"], "model.safetensors"), torch.float64)
-    plain = {r: P.forward(cfg, tensors, t, rnd=P.round_bf16 if bf16 else P.identity) for r, t in reqs.items()}
+    plain = {r: H.plain_logits_and_margins(cfg, dirs["B"], t, bf16) for r, t in reqs.items()}
+    n_cmp = n_all = 0
     for step, parts in expect:
         got = torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, V))
-        want = torch.cat([plain[r][pos] for r, pos in parts])
+        want = torch.cat([plain[r][0][pos] for r, pos in parts])
+        keep = torch.cat([H.decided(plain[r][1][pos], bf16) for r, pos in parts])
         assert got.shape == want.shape
-        assert H.rel_err(got, want) <= tol, f"step {step}: {H.rel_err(got, want):.3e}"
+        n_cmp, n_all = n_cmp + int(keep.sum()), n_all + keep.numel()
+        if keep.any():
+            assert H.rel_err(got[keep], want[keep]) <= tol, f"step {step}: {H.rel_err(got[keep], want[keep]):.3e}"
+    assert n_cmp >= 0.9 * n_all

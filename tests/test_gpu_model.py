@@ -36,16 +36,23 @@ _plain = {}
 
 
 def plain(name, model_dirs, tokens, bf16):
+    """(logits, positions to compare): see harness.ROUTER_GAP_BF16."""
     key = (name, tuple(tokens), bf16)
     if key not in _plain:
-        _plain[key] = H.plain_logits(CONFIGS[name][0], model_dirs[name], tokens, bf16)
+        lg, m = H.plain_logits_and_margins(CONFIGS[name][0], model_dirs[name], tokens, bf16)
+        keep = H.decided(m, bf16)
+        assert keep.all() or bf16, "a router near-tie at 32-bit level: choose other tokens"
+        assert keep.double().mean() >= 0.7, "too many router near-ties to test anything"
+        _plain[key] = (lg, keep)
     return _plain[key]
 
 
-def check(got, want, tol, what):
+def check(got, plain_result, tol, what):
+    want, keep = plain_result
+    got, want = got[keep], want[keep]
     e = H.rel_err(got, want)
     bad = H.first_bad_position(got, want, tol)
-    assert e <= tol, f"{what}: error {e:.3e} > {tol:.1e}; first wrong position {bad} of {want.shape[0]}"
+    assert e <= tol, f"{what}: error {e:.3e} > {tol:.1e}; first wrong position {bad} of {want.shape[0]} compared"
 
 
 DTYPES = [("float32", False, H.TOL_F32), ("bfloat16", True, H.TOL_BF16)]
@@ -129,27 +136,3 @@ def test_padding_changes_nothing(model_dirs, engines):
     b = eng.step([seqs[0], -1, seqs[1], -1], [toks[0], [0, 0, 0], toks[1], [5]], [[19], [], [8], []]).clone()
     eng.release(seqs)
     assert torch.equal(a, b)
-
-
-def test_moe_router_margin(model_dirs):
-    """The comparisons above are about arithmetic, not about which expert wins a near-tie:
-    on these models and requests the chosen and the first rejected expert are apart by more
-    than any rounding difference between the engine and the plain implementation."""
-    import plain_lfm3 as P
-    for name in ("B", "C"):
-        cfg = CONFIGS[name][0]
-        margins = []
-        orig = P.moe_route
-
-        def spy(h, wr, bias, k, norm_topk, scaling):
-            ids, w, c = orig(h, wr, bias, k, norm_topk, scaling)
-            cs = torch.sort(c, dim=-1, descending=True).values
-            margins.append(float((cs[:, k - 1] - cs[:, k]).min()))
-            return ids, w, c
-        P.moe_route = spy
-        try:
-            for toks in H.requests_for(cfg, LENGTHS[name], 11):
-                H.plain_logits(cfg, model_dirs[name], toks, True)
-        finally:
-            P.moe_route = orig
-        assert min(margins) > 5e-5, f"{name}: router margin {min(margins):.2e}"
