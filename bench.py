@@ -1,0 +1,307 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the LFM3 hybrid engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+Default run: the LFM2-1.2B-shaped configuration (16 layers: attention at 2, 5, 8, 10, 12, 14,
+short convolution elsewhere; hidden 2048, 32 heads, 8 kv heads, head size 64, feed-forward 5632,
+vocabulary 65536), bfloat16 random weights, batch 8, every sequence ending at context 4096.
+A step is one decode step of the whole batch.  One JSON line goes to stdout:
+
+  value      decoded tokens per second, timed on the device over K graph-replayed steps that feed
+             themselves (the chosen tokens become the next input on the device)
+  e2e        the same through the Python entry point (`Engine.generate`): host token ids in, host
+             token ids out, every step copying its inputs from pinned memory and reading its
+             tokens back
+  prefill    one prompt of 2,048 tokens: tokens/s, and the fraction of the bf16 peak
+  roofline   the bytes a decode step must read (every weight once, the cache of the live
+             sequences) over its time, against the measured copy bandwidth
+  points     decode tokens/s at batch 1 and 64, same context
+
+Weights (1.8 GB) are far larger than L2, so consecutive steps cannot be served from L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG_1P2B = {
+    "architectures": ["Lfm3ForCausalLM"], "model_type": "lfm3",
+    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
+    "layer_types": ["conv", "conv", "attention", "conv", "conv", "attention", "conv", "conv", "attention",
+                    "conv", "attention", "conv", "attention", "conv", "attention", "conv"],
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "intermediate_size": 8192, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+    "block_ffn_dim_multiplier": 1.0, "rope_theta": 1000000.0, "conv_L_cache": 3, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 128000,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            raw = json.load(f)
+        out = {k: float(raw[k]) for k in ("hbm_gbs", "bf16_tflops") if k in raw}
+        out["bf16_tflops_sustained"] = float(raw.get("bf16_tflops_sustained", out.get("bf16_tflops", 0)))
+        if "hbm_gbs" in out and "bf16_tflops" in out:
+            return out, "measured"
+    except (OSError, ValueError, KeyError, TypeError):
+        pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, lo: int = 0, hi: int | None = None) -> dict:
+        rows = self.rows[lo:hi] or self.rows
+        mhz = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def model_numbers(eng, cfg: dict) -> dict:
+    """Bytes and flops of a step, from the model's own tensors."""
+    import torch
+    from lastengine_b200.config import Lfm3Config
+    c = Lfm3Config.from_dict(cfg)
+    wbytes = eng.weight_bytes()
+    n_attn = len(c.attention_layers)
+    kv_bytes_per_token = n_attn * 2 * c.num_key_value_heads * c.head_dim * (2 if eng.dtype == torch.bfloat16 else 4)
+    state_bytes_per_seq = len(c.conv_layers) * c.hidden_size * (c.conv_L_cache - 1) * 4
+    D, F, V = c.hidden_size, c.ffn_dim, c.vocab_size
+    per_tok = 0
+    for kind in c.layer_types:
+        if kind == "conv":
+            per_tok += 2 * D * 3 * D + 2 * D * D
+        else:
+            per_tok += 2 * D * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim + 2 * c.num_attention_heads * c.head_dim * D
+        per_tok += 2 * D * 2 * F + 2 * F * D
+    return {"weight_bytes": wbytes, "kv_bytes_per_token": kv_bytes_per_token, "state_bytes_per_seq": state_bytes_per_seq,
+            "linear_flops_per_token": per_tok, "head_flops_per_row": 2 * D * V,
+            "attn_flops_per_qk": 4 * c.num_attention_heads * c.head_dim * n_attn}
+
+
+def time_prefill(eng, n_tokens: int, warmup: int, reps: int, rng) -> float:
+    import torch
+    toks = rng.integers(0, eng.vocab_size, size=n_tokens).tolist()
+    ms = []
+    for i in range(warmup + reps):
+        s = eng.new_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([s], [toks], "last")
+        b.record()
+        torch.cuda.synchronize()
+        eng.release(s)
+        if i >= warmup:
+            ms.append(a.elapsed_time(b))
+    return statistics.median(ms)
+
+
+def fill_context(eng, batch: int, length: int, rng, chunk: int = 8192) -> list[int]:
+    """`batch` sequences holding `length` random tokens each."""
+    seqs = [eng.new_sequence() for _ in range(batch)]
+    per = max(1, chunk // max(1, min(length, chunk)))
+    for lo in range(0, batch, per):
+        group = seqs[lo:lo + per]
+        done = 0
+        while done < length:
+            n = min(length - done, chunk)
+            eng.step(group, [rng.integers(0, eng.vocab_size, size=n).tolist() for _ in group], None)
+            done += n
+    return seqs
+
+
+def time_decode(eng, batch: int, context: int, steps: int, warmup: int, rng, clocks=None) -> dict:
+    """K self-feeding graph-replayed decode steps of `batch` sequences that end at `context`."""
+    import torch
+    from lastengine_b200.engine.graph import DecodeGraph
+    from lastengine_b200.sampling.params import SamplingParams
+    from lastengine_b200.sampling.sampler import Sampler
+    from lastengine_b200.ops import kernels
+    start_len = context - (steps + warmup + 1)
+    seqs = fill_context(eng, batch, start_len, rng)
+    total = steps + warmup + 1
+    g = DecodeGraph(eng, Sampler(SamplingParams(temperature=0.0), eng.device), batch,
+                    table_width=-(-context // eng.cache.page_size), self_feeding=True)
+    # room for every step of the run up front, so the page tables stay valid while the graph feeds itself
+    eng.cache.reserve({s: total for s in seqs})
+    grow = g.stage(seqs, rng.integers(0, eng.vocab_size, size=batch).tolist(), None)
+    g.launch()                                      # warm-up run + capture (the step has run once)
+    for _ in range(warmup):
+        g.launch()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    lo = clocks.mark() if clocks else 0
+    a.record()
+    for _ in range(steps):
+        g.launch()
+    b.record()
+    torch.cuda.synchronize()
+    hi = clocks.mark() if clocks else 0
+    ms = a.elapsed_time(b) / steps
+    eng.cache.commit({s: total for s in seqs})
+    avg_len = start_len + 1 + warmup + steps / 2
+    eng.release(seqs)
+    return {"ms_per_step": ms, "tok_s": batch * 1e3 / ms, "launches_per_step": g.launches,
+            "avg_context": avg_len, "clock_rows": (lo, hi)}
+
+
+def time_e2e(eng, batch: int, context: int, steps: int, rng) -> dict:
+    """The same decode through Engine.generate: host ids in, host ids out, every step."""
+    from lastengine_b200 import SamplingParams
+    prompts = [rng.integers(0, eng.vocab_size, size=context - steps - 1).tolist() for _ in range(batch)]
+    res = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=steps + 1, stop_token_ids=[],
+                       max_batch=batch, max_seq_len=context + 1)
+    st = res.stats
+    return {"value": st.decode_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": res.backend.h2d_bytes,
+            "d2h_bytes_per_step": res.backend.d2h_bytes, "decode_steps": st.decode_steps,
+            "prefill_tok_s": st.prefill_tok_s}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate (cargo, NVRTC); no Rust toolchain here, pip cannot install it "
+                          "('neither setup.py nor pyproject.toml'), and its GPU path reads only quantized GGUF files"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    from lastengine_b200 import Engine
+    from lastengine_b200.ops import kernels
+
+    cfg = dict(CONFIG_1P2B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers and args.layers < full_layers:
+        cfg["num_hidden_layers"] = args.layers
+        cfg["layer_types"] = cfg["layer_types"][:args.layers]
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    max_b = max(args.batch, 1 if args.skip_points else 64)
+    t0 = time.time()
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (args.context + 64) + 4096,
+                             max_seqs=max_b + 8)
+    nums = model_numbers(eng, cfg)
+    print(f"[bench] model ready in {time.time() - t0:.1f}s: {nums['weight_bytes'] / 1e9:.3f} GB of weights", file=sys.stderr)
+
+    clocks = ClockSampler()
+    clocks.start()
+    # ---- prefill ---------------------------------------------------------------------------
+    pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
+    pre_flops = (PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"]
+                 + nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
+    prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tokens/s",
+               "tflops": pre_flops / (pre_ms / 1e3) / 1e12}
+    print(f"[bench] prefill {PREFILL_TOKENS} tokens: {pre_ms:.3f} ms", file=sys.stderr)
+    # ---- decode ----------------------------------------------------------------------------
+    launches0 = kernels.launch_count()
+    main_run = time_decode(eng, args.batch, args.context, args.steps, args.warmup, rng, clocks)
+    launches = main_run["launches_per_step"] * args.steps
+    step_bytes = (nums["weight_bytes"] + args.batch * main_run["avg_context"] * nums["kv_bytes_per_token"]
+                  + 2 * args.batch * nums["state_bytes_per_seq"])
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    clk = clocks.summary(*main_run["clock_rows"])
+    print(f"[bench] decode b{args.batch}: {main_run['ms_per_step']:.4f} ms/step", file=sys.stderr)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = time_decode(eng, b, args.context, args.steps, args.warmup, rng)
+            points[f"decode_b{b}"] = r["tok_s"]
+            points[f"decode_b{b}_ms"] = r["ms_per_step"]
+            print(f"[bench] decode b{b}: {r['ms_per_step']:.4f} ms/step", file=sys.stderr)
+    e2e = None
+    if not args.skip_e2e:
+        e2e = time_e2e(eng, args.batch, args.context, args.steps, rng)
+        print(f"[bench] e2e b{args.batch}: {e2e['value']:.1f} tok/s", file=sys.stderr)
+    clocks.stop()
+
+    line = {
+        "metric": "decode tokens/s, batch 8 (LFM2-1.2B-shaped LFM3 hybrid, bf16, context 4096)",
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
+        "config": {"model": "LFM2-1.2B-shaped LFM3 hybrid", "global_batch": args.batch, "seq_len": args.context,
+                   "parallelism": "single GPU", "layers": cfg["num_hidden_layers"], "layers_in_config": full_layers,
+                   "attention_layers": sum(t != "conv" for t in cfg["layer_types"]), "hidden_size": 2048,
+                   "heads": 32, "kv_heads": 8, "head_dim": 64, "ffn": 5632, "vocab": 65536, "conv_L_cache": 3,
+                   "prefill_tokens": PREFILL_TOKENS, "weights_gb": round(nums["weight_bytes"] / 1e9, 3),
+                   "cache_defeat": "inputs larger than L2 (1.8 GB of weights per step)",
+                   "peaks": pk_src},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "of": pk_src, "bytes_per_step": step_bytes},
+        "points": points,
+        "gpu_launches": launches,
+        "clocks": clk,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -34,7 +34,7 @@ class CacheView:
     writable: bool
     page_size: int = PAGE_SIZE
     k: torch.Tensor | None = None            # [page, kv_head, page_size, head_dim]
-    v: torch.Tensor | None = None
+    v: torch.Tensor | None = None            # [page, kv_head, head_dim, page_size] (positions contiguous)
     block_table: torch.Tensor | None = None  # int32 [sequences of the step, pages]
     state: torch.Tensor | None = None        # [slot, *shape]
 
@@ -45,7 +45,8 @@ class KVGroup:
         self.spec, self.entries = spec, list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.page_size = page_size
-        self.pool = torch.empty((len(entries), 2, n_pages, spec.n_kv_heads, page_size, spec.head_dim),
+        # keys as [.., position, dim]; the value half is used as [.., dim, position] (same size)
+        self.pool = torch.zeros((len(entries), 2, n_pages, spec.n_kv_heads, page_size, spec.head_dim),
                                 dtype=dtype, device=device)
         self.pages = IdPool(n_pages, "cache page")
         self.seq_pages: dict[int, list[int]] = {}   # slot -> page of each page index (-1: given back)
@@ -182,7 +183,9 @@ class Cache:
         if kind == "kv":
             g = self.kv_groups[gi]
             i = g.index[entry]
-            return CacheView(writable=writable, page_size=self.page_size, k=g.pool[i, 0], v=g.pool[i, 1],
+            sp = g.spec
+            return CacheView(writable=writable, page_size=self.page_size, k=g.pool[i, 0],
+                             v=g.pool[i, 1].view(-1, sp.n_kv_heads, sp.head_dim, self.page_size),
                              block_table=tables[gi])
         g = self.state_groups[gi]
         return CacheView(writable=writable, page_size=self.page_size, state=g.data[g.index[entry]])

@@ -106,13 +106,14 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
     const int key0 = tile * 32;
     const int page = block_table[(size_t)b * bt_width + key0 / page_size];
     const size_t base = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * page_size + key0 % page_size) * hd;
+    const size_t vbase = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * hd * page_size + key0 % page_size;
     __syncthreads();  // the previous tile has been consumed (and q_s is written, first time round)
     for (int idx = threadIdx.x; idx < 32 * hd; idx += blockDim.x) {
       int kk = idx / hd, d = idx - kk * hd;
       float kv = 0.f, vv = 0.f;
       if (page >= 0 && key0 + kk < kv_len) {  // beyond the sequence the pool holds stale bits
         kv = to_f32(k_pool[base + idx]);
-        vv = to_f32(v_pool[base + idx]);
+        vv = to_f32(v_pool[vbase + (size_t)d * page_size + kk]);   // values are stored [dim][position]
       }
       k_s[kk * KS + d] = kv;
       v_s[idx] = vv;
@@ -243,7 +244,8 @@ static int launch_attention(void* out, float* part, const void* q, const void* k
   return 0;
 }
 
-// out, q: [M, nh*hd]; pools: [page][nkv][page_size][hd]; part: float scratch of
+// out, q: [M, nh*hd]; key pool [page][nkv][page_size][hd], value pool [page][nkv][hd][page_size];
+// part: float scratch of
 // M*nh*n_splits*(hd+2) elements, used when n_splits > 1 (then every sequence has one row).
 LEB_API int leb_attention(void* out, float* part, const void* q, const void* k_pool,
                           const void* v_pool, int dtype, const int* block_table, int bt_width,
@@ -290,5 +292,20 @@ LEB_API int leb_attention(void* out, float* part, const void* q, const void* k_p
       attention_merge_kernel<bf16><<<grid, 64, 0, st>>>((bf16*)out, part, (const bf16*)gate, gate_stride, nh, hd, n_splits);
     LEB_CHECK_LAUNCH("leb_attention merge");
   }
+  return 0;
+}
+
+// Merge of split partial results on its own (for kernels that write the same partial layout).
+LEB_API int leb_attention_merge(void* out, const float* part, int dtype, const void* gate,
+                                int gate_stride, int M, int nh, int hd, int n_splits, cudaStream_t st) {
+  if (M <= 0) return 0;
+  dim3 grid(M, nh);
+  if (dtype == LEB_F32)
+    attention_merge_kernel<float><<<grid, 64, 0, st>>>((float*)out, part, (const float*)gate, gate_stride, nh, hd, n_splits);
+  else if (dtype == LEB_BF16)
+    attention_merge_kernel<bf16><<<grid, 64, 0, st>>>((bf16*)out, part, (const bf16*)gate, gate_stride, nh, hd, n_splits);
+  else
+    return leb_fail("leb_attention_merge: unknown dtype %d", dtype);
+  LEB_CHECK_LAUNCH("leb_attention_merge");
   return 0;
 }

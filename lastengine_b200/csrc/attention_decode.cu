@@ -1,0 +1,284 @@
+// Decode attention on the tensor cores: one new token per sequence against its whole cache.
+//
+// A decode step reads every cached key and value of the live sequences once, so the kernel is
+// built around that stream (the reference's split-range decode kernels have the same aim,
+// src/cuda/dense.cu:152-237, with the query heads of a kv head sharing each key tile).  A block
+// owns one sequence, one kv head and one split of the key range; its 4 warps take blocks of 32
+// positions in turn, each with its own running (max, sum, acc), merged through shared memory at
+// the end; splits are merged by attention_merge_kernel (attention.cu).
+//
+// Both products run as mma.m16n8k16 with the G <= 16 query heads of the kv head as the 16 rows:
+//   S[head, pos]  = Q[head, :] . K[pos, :]         A = Q (registers), B = K rows from the cache
+//   O[head, dim] += P[head, pos] . V[pos, dim]     A = P (the S accumulators), B = V^T rows
+// Fragments come straight from global memory in 16-byte pieces, no shared-memory staging:
+//  * over head_dim, a lane's 8 contiguous values feed two k16 steps as pairs (0,1)(2,3) and
+//    (4,5)(6,7); Q uses the same assignment, and a dot product does not care about the order;
+//  * the value cache is stored [dim][position] per page, so a lane's 16 bytes are 8 positions of
+//    one dimension, which is what the second product contracts over;
+//  * score tile t of a block holds, in column n, position 8*(n/2) + 2t + (n%2): lane (r, c) then
+//    ends up with the probabilities of positions 8c..8c+7, exactly the 8 positions of its value
+//    piece, so S feeds the second product without any exchange between lanes.
+// Scores, maxima, exponentials and sums are float; P is rounded to bfloat16 for the second
+// product, as keys and values are.
+#include "common.cuh"
+
+#define ATD_WARPS 4
+#define ATD_NEG (-1e30f)
+
+__device__ __forceinline__ void mma16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// zero the 16-bit halves of a value piece whose positions are outside [lo, hi)
+__device__ __forceinline__ uint4 mask_positions(uint4 v, int first, int lo, int hi) {
+  uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    int p0 = first + 2 * i, p1 = p0 + 1;
+    uint32_t m = ((p0 >= lo && p0 < hi) ? 0x0000ffffu : 0u) | ((p1 >= lo && p1 < hi) ? 0xffff0000u : 0u);
+    w[i] &= m;
+  }
+  return v;
+}
+
+template <int HD>  // head_dim, a multiple of 32
+__global__ void __launch_bounds__(32 * ATD_WARPS)
+attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const bf16* __restrict__ q,
+                        const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ block_table, int bt_width,
+                        const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
+                        const int* __restrict__ seq_qstart, const bf16* __restrict__ gate,
+                        int gate_stride, int nh, int nkv, int page_size, int window, float scale,
+                        int n_splits) {
+  constexpr int KB = HD / 32;  // 32-wide pieces of head_dim
+  constexpr int NT = HD / 8;   // 8-wide output tiles over head_dim
+  __shared__ float o_s[ATD_WARPS][16][HD + 4];
+  __shared__ float m_s[ATD_WARPS][16], l_s[ATD_WARPS][16];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int G = nh / nkv;
+  const int slot = seq_slot[b];
+  const size_t m_row = seq_qstart[b];
+  const int h0 = kvh * G;
+
+  if (slot < 0) {  // padding sequence
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+      int hh = idx / HD, d = idx % HD;
+      if (n_splits == 1)
+        out[(m_row * nh + h0 + hh) * HD + d] = __float2bfloat16_rn(0.f);
+      else
+        part[((m_row * nh + h0 + hh) * n_splits + split) * (size_t)(HD + 2) + 2 + d] = 0.f;
+    }
+    if (n_splits > 1 && threadIdx.x < G) {
+      float* pp = part + ((m_row * nh + h0 + threadIdx.x) * n_splits + split) * (size_t)(HD + 2);
+      pp[0] = ATD_NEG;
+      pp[1] = 0.f;
+    }
+    return;
+  }
+
+  const int qpos = seq_pos0[b];
+  const int kv_len = qpos + 1;
+  const int key_lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
+  const int blk_first = key_lo / 32, blk_last = (kv_len - 1) / 32;
+  const int n_blk = blk_last - blk_first + 1;
+  const int per_split = (n_blk + n_splits - 1) / n_splits;
+  const int blk_lo = blk_first + split * per_split;
+  const int blk_hi = min(blk_last + 1, blk_lo + per_split);
+
+  // Q fragments: heads r and r+8 of this kv head (zero beyond G)
+  uint4 qa[KB], qb[KB];
+  {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const bf16* qrow = q + (m_row * nh + h0) * HD;
+#pragma unroll
+    for (int j = 0; j < KB; j++) {
+      qa[j] = r < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + 32 * j + 8 * c) : zero;
+      qb[j] = r + 8 < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)(r + 8) * HD + 32 * j + 8 * c) : zero;
+    }
+  }
+
+  float mx[2] = {ATD_NEG, ATD_NEG}, l[2] = {0.f, 0.f};
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; n++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc[n][e] = 0.f;
+
+  const int* table = block_table + (size_t)b * bt_width;
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS) {
+    const int key0 = blk * 32;
+    const int page = table[key0 / page_size];
+    const int off = key0 % page_size;
+    const bf16* kbase = k_pool + (((size_t)page * nkv + kvh) * page_size + off) * HD;
+    const bf16* vbase = v_pool + ((size_t)page * nkv + kvh) * HD * page_size + off;
+    // keys: tile t, column n = r -> position 8*(r/2) + 2t + (r%2)
+    uint4 kf[4][KB];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int kp = 8 * (r >> 1) + 2 * t + (r & 1);
+#pragma unroll
+      for (int j = 0; j < KB; j++)
+        kf[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
+    }
+    // values: output tile n, dimension 8n + r, positions 8c..8c+7 of the block
+    uint4 vf[NT];
+#pragma unroll
+    for (int n = 0; n < NT; n++)
+      vf[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+    const bool partial = key0 < key_lo || key0 + 32 > kv_len;
+    if (partial) {
+#pragma unroll
+      for (int n = 0; n < NT; n++) vf[n] = mask_positions(vf[n], key0 + 8 * c, key_lo, kv_len);
+    }
+
+    float s[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+#pragma unroll
+      for (int e = 0; e < 4; e++) s[t][e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < KB; j++) {
+        mma16816(s[t], qa[j].x, qb[j].x, qa[j].y, qb[j].y, kf[t][j].x, kf[t][j].y);
+        mma16816(s[t], qa[j].z, qb[j].z, qa[j].w, qb[j].w, kf[t][j].z, kf[t][j].w);
+      }
+    }
+    // s[t][0], s[t][1]: head r, positions key0 + 8c + 2t, +1;  s[t][2], s[t][3]: head r + 8
+    float tmax[2] = {ATD_NEG, ATD_NEG};
+#pragma unroll
+    for (int t = 0; t < 4; t++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int kp = key0 + 8 * c + 2 * t + (e & 1);
+        const bool valid = kp >= key_lo && kp < kv_len;
+        s[t][e] = valid ? s[t][e] * scale : ATD_NEG;
+        tmax[e >> 1] = fmaxf(tmax[e >> 1], s[t][e]);
+      }
+    float corr[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+      tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 1));
+      tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 2));
+      const float mn = fmaxf(mx[hh], tmax[hh]);
+      corr[hh] = expf(mx[hh] - mn);
+      mx[hh] = mn;
+    }
+    float psum[2] = {0.f, 0.f};
+    uint32_t pa[4][2];  // [tile][head r | head r+8] as bfloat16 pairs
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        p[e] = s[t][e] > 0.5f * ATD_NEG ? expf(s[t][e] - mx[e >> 1]) : 0.f;
+        psum[e >> 1] += p[e];
+      }
+      pa[t][0] = pack_bf16(p[0], p[1]);
+      pa[t][1] = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+      psum[hh] += __shfl_xor_sync(0xffffffffu, psum[hh], 1);
+      psum[hh] += __shfl_xor_sync(0xffffffffu, psum[hh], 2);
+      l[hh] = l[hh] * corr[hh] + psum[hh];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; n++) {
+      acc[n][0] *= corr[0];
+      acc[n][1] *= corr[0];
+      acc[n][2] *= corr[1];
+      acc[n][3] *= corr[1];
+      mma16816(acc[n], pa[0][0], pa[0][1], pa[1][0], pa[1][1], vf[n].x, vf[n].y);
+      mma16816(acc[n], pa[2][0], pa[2][1], pa[3][0], pa[3][1], vf[n].z, vf[n].w);
+    }
+  }
+
+  // merge the warps: acc[n][0..1] -> head r, dims 8n + 2c, +1; acc[n][2..3] -> head r + 8
+#pragma unroll
+  for (int n = 0; n < NT; n++) {
+    o_s[warp][r][8 * n + 2 * c] = acc[n][0];
+    o_s[warp][r][8 * n + 2 * c + 1] = acc[n][1];
+    o_s[warp][r + 8][8 * n + 2 * c] = acc[n][2];
+    o_s[warp][r + 8][8 * n + 2 * c + 1] = acc[n][3];
+  }
+  if (c == 0) {
+    m_s[warp][r] = mx[0];
+    l_s[warp][r] = l[0];
+    m_s[warp][r + 8] = mx[1];
+    l_s[warp][r + 8] = l[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int hh = idx / HD, d = idx % HD;
+    float M = ATD_NEG;
+#pragma unroll
+    for (int w = 0; w < ATD_WARPS; w++) M = fmaxf(M, m_s[w][hh]);
+    float L = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATD_WARPS; w++) {
+      const float f = expf(m_s[w][hh] - M);
+      L += l_s[w][hh] * f;
+      a += o_s[w][hh][d] * f;
+    }
+    const int h = h0 + hh;
+    if (n_splits == 1) {
+      float g = 1.f;
+      if (gate) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[m_row * gate_stride + h])));
+      out[(m_row * nh + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? a / L * g : 0.f);
+    } else {
+      float* pp = part + ((m_row * nh + h) * n_splits + split) * (size_t)(HD + 2);
+      if (d == 0) { pp[0] = M; pp[1] = L; }
+      pp[2 + d] = a;
+    }
+  }
+}
+
+// Returns 1 when the sizes are ones this kernel takes (the caller then uses the general kernel).
+LEB_API int leb_attention_decode_supported(int nh, int nkv, int hd, int page_size) {
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16) return 0;
+  if (hd != 32 && hd != 64 && hd != 96 && hd != 128) return 0;
+  return page_size % 32 == 0;
+}
+
+// The first stage of a decode step's attention: every sequence brings one row.  With
+// n_splits > 1 the partial results go to `part` (same layout as the general kernel's) and the
+// caller merges them.
+LEB_API int leb_attention_decode(void* out, float* part, const void* q, const void* k_pool,
+                                 const void* v_pool, const int* block_table, int bt_width,
+                                 const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
+                                 const void* gate, int gate_stride, int B, int nh, int nkv, int hd,
+                                 int page_size, int window, float scale, int n_splits,
+                                 cudaStream_t st) {
+  if (B <= 0) return 0;
+  LEB_REQUIRE(leb_attention_decode_supported(nh, nkv, hd, page_size),
+              "leb_attention_decode: sizes not taken (heads %d, kv heads %d, head_dim %d, page %d)", nh, nkv, hd, page_size);
+  LEB_REQUIRE(n_splits >= 1 && (n_splits == 1 || part), "leb_attention_decode: splits need scratch");
+  dim3 grid(nkv, B, n_splits);
+  LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_decode: grid too large");
+#define LEB_ATD(HD_)                                                                              \
+  attention_decode_kernel<HD_><<<grid, 32 * ATD_WARPS, 0, st>>>(                                  \
+      (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,    \
+      bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
+      window, scale, n_splits)
+  switch (hd) {
+    case 32: LEB_ATD(32); break;
+    case 64: LEB_ATD(64); break;
+    case 96: LEB_ATD(96); break;
+    default: LEB_ATD(128); break;
+  }
+#undef LEB_ATD
+  LEB_CHECK_LAUNCH("leb_attention_decode");
+  return 0;
+}

@@ -16,10 +16,14 @@ enum LebDtype { LEB_F32 = 0, LEB_BF16 = 1 };
 
 int leb_fail(const char* fmt, ...);  // records the message, returns 1
 
+// Kernels launched by this library since it was loaded (each check stands for one launch).
+extern long long g_leb_launches;
+
 #define LEB_CHECK_LAUNCH(name)                                                        \
   do {                                                                                \
     cudaError_t e_ = cudaGetLastError();                                              \
     if (e_ != cudaSuccess) return leb_fail("%s: %s", name, cudaGetErrorString(e_));   \
+    g_leb_launches++;                                                                 \
   } while (0)
 
 #define LEB_REQUIRE(cond, ...)                 \

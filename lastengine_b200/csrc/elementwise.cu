@@ -16,6 +16,9 @@ int leb_fail(const char* fmt, ...) {
 }
 LEB_API const char* leb_last_error() { return g_err; }
 
+long long g_leb_launches = 0;
+LEB_API long long leb_launch_count() { return g_leb_launches; }
+
 // ---------------------------------------------------------------------------------------------
 // x[m, :] = table[tokens[m], :]            (reference: src/dense.rs:172-177 takes the row as is)
 template <typename T>

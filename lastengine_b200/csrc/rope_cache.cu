@@ -10,8 +10,10 @@
 // (src/cuda/dense.cu:80-93); here the same launch also serves prompts.
 // Norm, angle, sine and cosine are float; sinf/cosf are the full-range versions.
 //
-// Cache layout of one layer: [page][kv_head][page_size][head_dim]; the page of position p of
-// sequence b is block_table[b][p / page_size].
+// Cache layout of one layer: keys [page][kv_head][page_size][head_dim]; values transposed,
+// [page][kv_head][head_dim][page_size], so that the positions of a page are contiguous for each
+// dimension (the tensor-core attention kernels contract over positions and read them 8 at a
+// time).  The page of position p of sequence b is block_table[b][p / page_size].
 #include "common.cuh"
 
 template <typename T, typename CT>
@@ -85,9 +87,13 @@ __global__ void qk_rope_store_kernel(
     int kvh = kind == 1 ? head - nh : head - nh - nkv;
     int page = block_table[(size_t)b * bt_width + pos / page_size];
     if (page < 0) return;  // a position the cache no longer holds (outside a window)
-    CT* pool = kind == 1 ? k_pool : v_pool;
-    CT* o = pool + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
-    for (int i = lane; i < hd; i += 32) o[i] = from_f32<CT>(v[i]);
+    if (kind == 1) {
+      CT* o = k_pool + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
+      for (int i = lane; i < hd; i += 32) o[i] = from_f32<CT>(v[i]);
+    } else {
+      CT* o = v_pool + ((size_t)page * nkv + kvh) * hd * page_size + pos % page_size;
+      for (int i = lane; i < hd; i += 32) o[(size_t)i * page_size] = from_f32<CT>(v[i]);
+    }
   }
 }
 

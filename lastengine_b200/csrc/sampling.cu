@@ -194,3 +194,24 @@ LEB_API int leb_sample(int* out, const float* logits, const float* u01, int n, i
   LEB_CHECK_LAUNCH("leb_sample");
   return 0;
 }
+
+// After a decode step whose tokens were chosen on the device: the chosen tokens become the
+// next step's input and every live sequence moves one position on, so the same launch
+// sequence (a captured graph) can run again without the host.
+__global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_pos,
+                               int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
+                               const int* __restrict__ chosen, int B) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B || seq_slot[b] < 0) return;
+  tokens[b] = chosen[b];
+  row_pos[b] += 1;
+  seq_pos0[b] += 1;
+}
+
+LEB_API int leb_advance(int* tokens, int* row_pos, int* seq_pos0, const int* seq_slot,
+                        const int* chosen, int B, cudaStream_t st) {
+  if (B <= 0) return 0;
+  advance_kernel<<<ceil_div(B, 128), 128, 0, st>>>(tokens, row_pos, seq_pos0, seq_slot, chosen, B);
+  LEB_CHECK_LAUNCH("leb_advance");
+  return 0;
+}

@@ -1,0 +1,124 @@
+"""Decode steps as captured CUDA graphs.
+
+A decode step is a fixed sequence of launches whose arguments do not change from token to
+token: positions, slots and page tables live in device memory that the host refreshes with
+one copy before each replay.  The reference captures its decode layer loop the same way, with
+the position in device memory (src/gpu/dense.rs:270-337, :21).  One graph per batch-size
+bucket; a batch smaller than its bucket is filled up with padding sequences, which change no
+result.  Each bucket has scratch memory of its own, so prompts of any size between two decode
+steps cannot move what a graph points at.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..ops import kernels
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .batch import BatchBuilder
+from .generate import EngineBackend
+from .workspace import Workspace
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def bucket_for(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return -(-n // 256) * 256
+
+
+class DecodeGraph:
+    """The captured step of one bucket: forward pass, choice of the next tokens, and (for runs
+    that feed themselves) the move to the next position."""
+
+    def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False):
+        self.engine, self.sampler, self.bucket, self.width = engine, sampler, bucket, table_width
+        self.self_feeding = self_feeding
+        self.ws = Workspace(engine.device)
+        self.builder = BatchBuilder(engine.device)
+        self.out = torch.zeros(bucket, dtype=torch.int32, device=engine.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.batch = None
+        self.launches = 0
+
+    def _run(self, batch) -> None:
+        eng = self.engine
+        logits = eng.model.forward(batch, eng.cache)
+        self.sampler.sample(self.out, logits, batch.u01)
+        if self.self_feeding:
+            kernels.advance(batch, self.out)
+
+    def stage(self, slots: list[int], tokens: list[int], u01) -> dict[int, int]:
+        """Lays the step's inputs out in this bucket's fixed device buffers (one copy)."""
+        eng = self.engine
+        pad = self.bucket - len(slots)
+        seqs = list(slots) + [-1] * pad
+        toks = [[t] for t in tokens] + [[0]] * pad
+        u = None
+        if self.sampler.needs_uniform():
+            u = np.zeros(self.bucket, dtype=np.float32)
+            u[:len(slots)] = u01
+        batch, grow = eng.prepare(seqs, toks, "last", u01=u, builder=self.builder, table_width=self.width)
+        if self.batch is not None:
+            same = (batch.tokens.data_ptr() == self.batch.tokens.data_ptr()
+                    and all(batch.tables[k].data_ptr() == self.batch.tables[k].data_ptr() for k in batch.tables))
+            if not same:
+                self.graph = None      # the staging buffer moved: capture again
+        self.batch = batch
+        return grow
+
+    def launch(self) -> None:
+        eng = self.engine
+        saved = eng.env.workspace
+        eng.env.workspace = self.ws
+        try:
+            if self.graph is None or self.ws_generation != self.ws.generation:
+                self._run(self.batch)            # warm-up: loads kernels, sizes the scratch memory
+                torch.cuda.current_stream().synchronize()
+                before = kernels.launch_count()
+                g = torch.cuda.CUDAGraph()
+                self.ws.frozen = True
+                try:
+                    with torch.cuda.graph(g):
+                        self._run(self.batch)
+                finally:
+                    self.ws.frozen = False
+                self.launches = kernels.launch_count() - before
+                self.graph, self.ws_generation = g, self.ws.generation
+                # capturing executes nothing and the warm-up ran the step: it has run exactly once
+            else:
+                self.graph.replay()
+        finally:
+            eng.env.workspace = saved
+
+
+class GraphBackend(EngineBackend):
+    """The generation loop's backend with graph-replayed decode steps."""
+
+    def __init__(self, engine, sampling: SamplingParams, max_batch: int = 64, max_seq_len: int | None = None):
+        super().__init__(engine, sampling)
+        self.graphs: dict[int, DecodeGraph] = {}
+        page = engine.cache.page_size
+        self.width = -(-(max_seq_len or engine.max_tokens) // page)
+        self.h2d_bytes = 0
+
+    def decode(self, slots, tokens, u01, histories):
+        if self.sampler.params.has_penalties:
+            return super().decode(slots, tokens, u01, histories)
+        eng = self.engine
+        b = bucket_for(len(slots))
+        g = self.graphs.get(b)
+        if g is None:
+            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width)
+        grow = g.stage(slots, tokens, u01)
+        g.launch()
+        eng.cache.commit(grow)
+        n = len(slots)
+        self._host[:n].copy_(g.out[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.h2d_bytes = g.builder.last_h2d_bytes
+        self.d2h_bytes = n * 4
+        return self._host[:n].tolist()

@@ -46,11 +46,17 @@ def _declare(L) -> None:
         "leb_penalties": [P, P, P, I, I, I, F, F, P],
         "leb_argmax": [P, P, I, I, P],
         "leb_sample": [P, P, P, I, I, I, F, F, F, P],
+        "leb_advance": [P, P, P, P, P, I, P],
+        "leb_attention_decode_supported": [I, I, I, I],
+        "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+        "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
         fn.argtypes = args
         fn.restype = c_int
+    L.leb_launch_count.restype = ctypes.c_longlong
+    L.leb_launch_count.argtypes = []
     for name, args in _OPTIONAL.items():
         fn = getattr(L, name, None)
         if fn is not None:
@@ -190,7 +196,7 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
         kv_stride = k_in.stride(0)
         _cuda(k_pool, "qk_rope_store.k_pool", q_out.dtype)
         _cuda(v_pool, "qk_rope_store.v_pool", q_out.dtype)
-        assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape == k_pool.shape
+        assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, hd, page_size)
     _cuda(block_table, "qk_rope_store.block_table", torch.int32)
     for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
         if t is not None:
@@ -208,8 +214,8 @@ def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
     """How many blocks share one sequence's key range in a decode step (1 for prompts)."""
     if batch.max_qlen != 1:
         return 1
-    per = batch.n_seqs * nkv * ((G + 7) // 8)
-    return max(1, min(16, (2 * sm_count) // max(per, 1)))
+    per = batch.n_seqs * nkv * ((G + 15) // 16)
+    return max(1, min(32, (2 * sm_count) // max(per, 1)))
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -224,7 +230,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     _cuda(block_table, "attention.block_table", torch.int32)
     M = out.shape[0]
     assert out.shape == (M, nh * hd) and q.shape == (M, nh * hd)
-    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape == k_pool.shape
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, hd, page_size)
     gate_stride = 0
     if gate is not None:
         _cuda(gate, "attention.gate", out.dtype, contiguous=False)
@@ -235,7 +241,20 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention: {n_splits} splits need {need} floats of scratch")
         _cuda(scratch, "attention.scratch", torch.float32)
-    _check(lib().leb_attention(
+    L = lib()
+    if (out.dtype == torch.bfloat16 and batch.max_qlen == 1 and M == batch.n_seqs
+            and L.leb_attention_decode_supported(nh, nkv, hd, page_size)):
+        # one row per sequence: the tensor-core decode kernel, then the merge of its splits
+        _check(L.leb_attention_decode(
+            _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+            block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),
+            _ptr(gate), gate_stride, batch.n_seqs, nh, nkv, hd, page_size, window, float(scale), n_splits,
+            _stream()))
+        if n_splits > 1:
+            _check(L.leb_attention_merge(_ptr(out), _ptr(scratch), BF16, _ptr(gate), gate_stride, M, nh, hd,
+                                         n_splits, _stream()))
+        return
+    _check(L.leb_attention(
         _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention"),
         _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
         _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(gate), gate_stride, M, batch.n_seqs, nh, nkv,
@@ -366,3 +385,16 @@ def sample(out: torch.Tensor, logits: torch.Tensor, u01: torch.Tensor, top_k: in
     assert out.numel() >= n and u01.numel() >= n
     _check(lib().leb_sample(_ptr(out), _ptr(logits), _ptr(u01), n, V, int(top_k), float(temperature),
                             float(top_p), float(min_p), _stream()))
+
+
+def advance(batch, chosen: torch.Tensor) -> None:
+    """The chosen tokens become the step's input and every live sequence moves one position on."""
+    _cuda(chosen, "advance.chosen", torch.int32)
+    _check(lib().leb_advance(_ptr(batch.tokens), _ptr(batch.row_pos), _ptr(batch.seq_pos0), _ptr(batch.seq_slot),
+                             _ptr(chosen), batch.n_seqs, _stream()))
+
+
+def launch_count() -> int:
+    """Kernels this library has launched in this process (launches inside a replayed graph are
+    counted once, when the graph was captured)."""
+    return int(lib().leb_launch_count())

@@ -192,7 +192,7 @@ def test_qk_rope_store(dtype, nh, nkv, hd, rope_dim):
     n_pages = 8
     tables = {0: np.array([[5, 2, -1], [1, 7, 3]], dtype=np.int32)}
     kp = torch.zeros(n_pages, nkv, page, hd, device=DEV, dtype=dtype)
-    vp = torch.zeros_like(kp)
+    vp = torch.zeros(n_pages, nkv, hd, page, device=DEV, dtype=dtype)      # values: positions contiguous
     batch = builder().build([0, 1], [[0] * n for n in lens], pos0, [], tables)
     q_out = torch.empty(M, nh * hd, device=DEV, dtype=dtype)
     qd = qkv.to(DEV)
@@ -210,7 +210,7 @@ def test_qk_rope_store(dtype, nh, nkv, hd, rope_dim):
         for i, p_ in enumerate(pos.tolist()):
             pg = int(tables[0][b, p_ // page])
             assert err(kp[pg, :, p_ % page, :], k[i]) < tol
-            assert err(vp[pg, :, p_ % page, :], v[i]) < tol
+            assert err(vp[pg, :, :, p_ % page], v[i]) < tol
         r0 += n
 
 
@@ -234,15 +234,15 @@ def plain_attention(q, k, v, qpos, window, scale):
 def fill_cache(k, v, pages, nkv, hd, page, dtype):
     n_pages = max(pages) + 2
     kp = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)   # unused places hold NaN
-    vp = torch.full_like(kp, float("nan"))
+    vp = torch.full((n_pages, nkv, hd, page), float("nan"), dtype=dtype)   # values: positions contiguous
     for t in range(k.shape[0]):
         kp[pages[t // page], :, t % page] = k[t].to(dtype)
-        vp[pages[t // page], :, t % page] = v[t].to(dtype)
+        vp[pages[t // page], :, :, t % page] = v[t].to(dtype)
     return kp.to(DEV), vp.to(DEV)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 48), (10, 5, 80), (16, 1, 32), (8, 8, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 48), (10, 5, 80), (16, 1, 32), (8, 8, 128), (32, 8, 64), (12, 2, 96)])
 @pytest.mark.parametrize("window", [0, 40])
 def test_attention_prompt_and_decode(dtype, nh, nkv, hd, window):
     page, Tk = 64, 150
@@ -300,12 +300,12 @@ def test_attention_batch_of_unequal_sequences():
     ks = [gen(n, nkv, hd, seed=60 + i) for i, n in enumerate(lens_k)]
     vs = [gen(n, nkv, hd, seed=70 + i) for i, n in enumerate(lens_k)]
     pools_k = torch.full((12, nkv, page, hd), float("nan"))
-    pools_v = torch.full_like(pools_k, float("nan"))
+    pools_v = torch.full((12, nkv, hd, page), float("nan"))
     page_lists = [[7, 2], [9], [0, 11, 4]]
     for i in range(3):
         for t in range(lens_k[i]):
             pools_k[page_lists[i][t // page], :, t % page] = ks[i][t]
-            pools_v[page_lists[i][t // page], :, t % page] = vs[i][t]
+            pools_v[page_lists[i][t // page], :, :, t % page] = vs[i][t]
     table = np.full((4, 3), -1, dtype=np.int32)
     for i, pl in enumerate(page_lists):
         table[i if i < 2 else 3, :len(pl)] = pl

@@ -119,7 +119,7 @@ def test_attention_part(dtype, rnd, tol, window, gate):
     hdv = h.to(device=DEV, dtype=dtype)
     for lo, hi in ((0, 70), (70, 71), (71, 100)):       # a prompt, one token, another chunk
         b = one_sequence_batch(hi - lo, lo, table=table)
-        view = CacheView(writable=True, k=pool[0], v=pool[1], block_table=b.tables[0])
+        view = CacheView(writable=True, k=pool[0], v=pool[1].view(4, nkv, hd, 64), block_table=b.tables[0])
         part.forward(hdv[lo:hi], out[lo:hi], False, b, view, env)
     want = P.attention(h, w, T, nh=nh, nkv=nkv, hd=hd, eps=1e-4, theta=5e4, rope_dim=32, window=window,
                        gate=gate, rnd=rnd)
