@@ -50,6 +50,10 @@ def _declare(L) -> None:
         "leb_attention_decode_supported": [I, I, I, I],
         "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
+        "leb_attention_prefill_supported": [I, I, I, I],
+        "leb_attention_prefill": [P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+        "leb_gemm_bf16_tc_supported": [P, P, I, I],
+        "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -254,6 +258,15 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
             _check(L.leb_attention_merge(_ptr(out), _ptr(scratch), BF16, _ptr(gate), gate_stride, M, nh, hd,
                                          n_splits, _stream()))
         return
+    if (out.dtype == torch.bfloat16 and n_splits == 1
+            and L.leb_attention_prefill_supported(nh, nkv, hd, page_size)):
+        # rows of prompts (or decode without splits): the tensor-core kernel over (position, head) rows
+        _check(L.leb_attention_prefill(
+            _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+            _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart), _ptr(batch.seq_qlen),
+            _ptr(gate), gate_stride, batch.n_seqs, nh, nkv, hd, page_size, window, float(scale),
+            batch.max_qlen, _stream()))
+        return
     _check(L.leb_attention(
         _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention"),
         _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
@@ -267,12 +280,14 @@ SMALL_M = 64  # rows up to which the weight-streaming kernel is used
 
 
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
-           group_offsets: torch.Tensor | None = None, rows_hint: int = 0) -> None:
+           group_offsets: torch.Tensor | None = None, rows_hint: int = 0, streaming: bool = False) -> None:
     """out (+)= x . w^T  with w [N, K] (or [E, N, K] with group_offsets [E+1] over the rows).
 
     float32 operands run on the CUDA cores in true 32-bit; bfloat16 operands on the tensor
     cores with float accumulation.  `epilogue`: STORE, ACCUMULATE (out is the float residual)
     or SWIGLU (w holds gate and up rows interleaved in blocks of 16; out has N/2 columns).
+    With more than SMALL_M rows bfloat16 products go to the tcgen05 kernel, unless `streaming`
+    asks for the weight-streaming kernel whatever the row count.
     """
     _cuda(x, "linear.x", contiguous=False)
     _cuda(w, "linear.w", x.dtype)
@@ -306,7 +321,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
         raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
     hint = rows_hint if rows_hint > 0 else M
     tc = _OPTIONAL_TC[0]
-    if tc is not None and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
+    if tc is not None and not streaming and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
         return
     _check(L.leb_gemm_bf16_small(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
                                  epilogue, _ptr(group_offsets), E, stride, hint, _stream()))
@@ -398,3 +413,39 @@ def launch_count() -> int:
     """Kernels this library has launched in this process (launches inside a replayed graph are
     counted once, when the graph was captured)."""
     return int(lib().leb_launch_count())
+
+
+# ---- the tcgen05 matrix product ----------------------------------------------------------------
+_tc_status: dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _tc_status:
+        _tc_status[i] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[i]
+
+
+def check_device_status() -> None:
+    """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
+    for i, t in _tc_status.items():
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise KernelError(f"a tensor-core matrix product gave up waiting (role {v}) on cuda:{i}; "
+                              "its result is not valid")
+
+
+def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE) -> bool:
+    """out (+)= x . w^T on tcgen05 with TMA-fed tiles; False when the operands cannot go through TMA."""
+    L = lib()
+    M, K = x.shape
+    N = w.shape[0]
+    if not L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, x.stride(0)):
+        return False
+    _check(L.leb_gemm_bf16_tc(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
+                              out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
+    return True
+
+
+_OPTIONAL_TC[0] = linear_tc

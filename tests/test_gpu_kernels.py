@@ -99,17 +99,17 @@ def test_linear_bf16_small(M, N, K_):
     x, w = gen(M, K_, seed=9, dtype=torch.bfloat16), gen(N, K_, seed=10, dtype=torch.bfloat16)
     want = x.double() @ w.double().T
     out = torch.empty(M, N, device=DEV)
-    K().linear(out, x.to(DEV), w.to(DEV))
+    K().linear(out, x.to(DEV), w.to(DEV), streaming=True)
     assert err(out, want) < 1e-5
     ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    K().linear(ob, x.to(DEV), w.to(DEV))
+    K().linear(ob, x.to(DEV), w.to(DEV), streaming=True)
     assert err(ob, want) < 5e-3
     base = gen(M, N, seed=11).to(DEV)
     b0 = base.clone()
-    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE, streaming=True)
     assert err(base, b0.cpu().double() + want) < 1e-5
     one = torch.empty(1, N, device=DEV)
-    K().linear(one, x[M - 1:].to(DEV), w.to(DEV))
+    K().linear(one, x[M - 1:].to(DEV), w.to(DEV), streaming=True)
     assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
@@ -121,7 +121,7 @@ def test_linear_bf16_swiglu_epilogue(M, F, D):
     want = P.silu(x.double() @ w1.double().T) * (x.double() @ w3.double().T)
     w13 = fuse_gate_up(w1, w3, True).to(DEV)
     out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
-    K().linear(out, x.to(DEV), w13, K().SWIGLU)
+    K().linear(out, x.to(DEV), w13, K().SWIGLU, streaming=True)
     assert err(out, want) < 6e-3
 
 
@@ -293,14 +293,15 @@ def test_attention_far_key_and_window_edge(dtype):
             assert hit == sees, (splits, window)
 
 
-def test_attention_batch_of_unequal_sequences():
+@pytest.mark.parametrize("dtype,nh,nkv,hd", [(torch.float32, 6, 2, 48), (torch.bfloat16, 6, 2, 64), (torch.bfloat16, 6, 2, 48)])
+def test_attention_batch_of_unequal_sequences(dtype, nh, nkv, hd):
     """Several sequences in one launch, each with its own pages, lengths and row counts; one is padding."""
-    dtype, nh, nkv, hd, page = torch.float32, 6, 2, 48, 64
+    page = 64
     lens_k, pos0, qn = [90, 10, 130], [60, 0, 129], [30, 10, 1]
-    ks = [gen(n, nkv, hd, seed=60 + i) for i, n in enumerate(lens_k)]
-    vs = [gen(n, nkv, hd, seed=70 + i) for i, n in enumerate(lens_k)]
-    pools_k = torch.full((12, nkv, page, hd), float("nan"))
-    pools_v = torch.full((12, nkv, hd, page), float("nan"))
+    ks = [gen(n, nkv, hd, seed=60 + i, dtype=dtype) for i, n in enumerate(lens_k)]
+    vs = [gen(n, nkv, hd, seed=70 + i, dtype=dtype) for i, n in enumerate(lens_k)]
+    pools_k = torch.full((12, nkv, page, hd), float("nan"), dtype=dtype)
+    pools_v = torch.full((12, nkv, hd, page), float("nan"), dtype=dtype)
     page_lists = [[7, 2], [9], [0, 11, 4]]
     for i in range(3):
         for t in range(lens_k[i]):
@@ -310,10 +311,10 @@ def test_attention_batch_of_unequal_sequences():
     for i, pl in enumerate(page_lists):
         table[i if i < 2 else 3, :len(pl)] = pl
     slots, rows = [0, 1, -1, 2], [qn[0], qn[1], 2, qn[2]]
-    qs = [gen(n, nh, hd, seed=80 + i) for i, n in enumerate(rows)]
+    qs = [gen(n, nh, hd, seed=80 + i, dtype=dtype) for i, n in enumerate(rows)]
     batch = builder().build(slots, [[0] * n for n in rows], [pos0[0], pos0[1], 0, pos0[2]], [], {0: table})
     M = sum(rows)
-    out = torch.empty(M, nh * hd, device=DEV)
+    out = torch.empty(M, nh * hd, device=DEV, dtype=dtype)
     K().attention(out, torch.cat(qs).reshape(M, nh * hd).to(DEV), pools_k.to(DEV), pools_v.to(DEV), batch.tables[0],
                   batch, nh, nkv, hd, page, 0, 0.2)
     r0 = 0
@@ -321,7 +322,7 @@ def test_attention_batch_of_unequal_sequences():
         if s >= 0:
             p0 = [pos0[0], pos0[1], 0, pos0[2]][j]
             want = plain_attention(qs[j].double(), ks[s].double(), vs[s].double(), torch.arange(p0, p0 + n), 0, 0.2)
-            assert err(out[r0:r0 + n].view(n, nh, hd), want) < 2e-5
+            assert err(out[r0:r0 + n].view(n, nh, hd), want) < (2e-5 if dtype == torch.float32 else 8e-3)
         else:
             assert float(out[r0:r0 + n].abs().max()) == 0.0
         r0 += n
@@ -388,3 +389,54 @@ def test_penalties():
     ld = logits.to(DEV)
     K().penalties(ld, hist.to(DEV), ln.to(DEV), 1.3, 0.2)
     assert err(ld, want) < 1e-6
+
+
+# ---- the tcgen05 matrix product ------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (128, 256, 128), (65, 48, 72), (200, 100, 200), (300, 520, 136),
+                                    (2048, 2048, 2048), (513, 6144, 2048), (1000, 2048, 5632)])
+def test_linear_tc(M, N, K_):
+    """Tensor-memory accumulation against float64, at tile-aligned sizes and at sizes where rows,
+    columns and k all run past the last tile; store, add-to-residual, and both result types."""
+    x, w = gen(M, K_, seed=100, dtype=torch.bfloat16), gen(N, K_, seed=101, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    assert K().linear_tc(out, x.to(DEV), w.to(DEV))
+    K().check_device_status()
+    assert err(out, want) < 2e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear_tc(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=102).to(DEV)
+    b0 = base.clone()
+    K().linear_tc(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    K().check_device_status()
+    assert err(base, b0.cpu().double() + want) < 2e-5
+
+
+@pytest.mark.parametrize("M,F,D", [(128, 64, 64), (70, 16, 40), (300, 160, 96), (2048, 5632, 2048)])
+def test_linear_tc_swiglu_epilogue(M, F, D):
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    x = gen(M, D, seed=103, dtype=torch.bfloat16)
+    w1, w3 = gen(F, D, seed=104, scale=0.05, dtype=torch.bfloat16), gen(F, D, seed=105, scale=0.05, dtype=torch.bfloat16)
+    want = P.silu(x.double() @ w1.double().T) * (x.double() @ w3.double().T)
+    w13 = fuse_gate_up(w1, w3, True).to(DEV)
+    out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    assert K().linear_tc(out, x.to(DEV), w13, K().SWIGLU)
+    K().check_device_status()
+    assert err(out, want) < 6e-3
+
+
+def test_linear_tc_strided_operand_and_small_kernel_agree():
+    """A column slice as the left operand (row stride larger than its width), and agreement with the
+    weight-streaming kernel on the same product."""
+    M, N, K_ = 150, 96, 128
+    big = gen(M, 3 * K_, seed=106, dtype=torch.bfloat16).to(DEV)
+    x = big[:, K_:2 * K_]
+    w = gen(N, K_, seed=107, dtype=torch.bfloat16).to(DEV)
+    a = torch.empty(M, N, device=DEV)
+    b = torch.empty(M, N, device=DEV)
+    assert K().linear_tc(a, x, w)
+    K().lib().leb_gemm_bf16_small(b.data_ptr(), 0, x.data_ptr(), w.data_ptr(), M, N, K_, x.stride(0), N, 0, None, 1, 0, M,
+                                  torch.cuda.current_stream().cuda_stream)
+    assert err(a, x.double().cpu() @ w.double().cpu().T) < 2e-5
+    assert err(a, b) < 2e-6
