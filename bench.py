@@ -214,6 +214,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--only-prefill", action="store_true", help="time the prompt step only (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -256,6 +257,10 @@ def main() -> int:
                "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tokens/s",
                "tflops": pre_flops / (pre_ms / 1e3) / 1e12}
     print(f"[bench] prefill {PREFILL_TOKENS} tokens: {pre_ms:.3f} ms", file=sys.stderr)
+    if args.only_prefill:
+        clocks.stop()
+        print(json.dumps({"prefill": prefill}))
+        return 0
     # ---- decode ----------------------------------------------------------------------------
     launches0 = kernels.launch_count()
     main_run = time_decode(eng, args.batch, args.context, args.steps, args.warmup, rng, clocks)

@@ -114,7 +114,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 }
 
 template <typename TC, int BN, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -183,41 +183,76 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // epilogue warps: tensor-memory lanes 32*(warp%4) .. +31 are rows of the tile
     const int quad = warp & 3;
-    const int row = m0 + quad * 32 + lane;
+    // Each warp stages its 32 rows of a 32-column piece in shared memory (the pipeline's first
+    // stage, free once the accumulator is complete) and writes them out row by row, so that a
+    // store covers whole 128-byte lines instead of one element in each of 32 rows.
+    float* stg = reinterpret_cast<float*>(smem) + quad * (32 * 36);
+    const int row_base = m0 + quad * 32;
     bool ok = mbar_wait(acc_full, 0, abort_flag);
     if (!ok && lane == 0) atomicExch(status, 3);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // the warp leaves together
     tc_fence_after();
     if (ok) {
+      const int ncols = epilogue == 2 ? 16 : 32;          // output columns per piece
+      const int n_out = epilogue == 2 ? N / 2 : N;
+      const int lpr = ncols / 4, rpp = 32 / lpr;          // lanes per row, rows per pass
+      const int lr = lane / lpr, lc = (lane % lpr) * 4;
+      const bool vec = (ldc % 4 == 0) && (((uintptr_t)C % 16) == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
-        if (row < M) {
-          if (epilogue == 2) {
-            // columns c0..c0+15 gate, c0+16..c0+31 up of outputs (n0 + c0)/2 + i
-            const int j0 = (n0 + c0) >> 1;
-            TC* o = C + (size_t)row * ldc + j0;
+        float* mine = stg + lane * 36;
+        if (epilogue == 2) {
+          // columns c0..c0+15 gate, c0+16..c0+31 up of outputs (n0 + c0)/2 + i
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-              if (2 * (j0 + i) < N) {
-                const float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
-                o[i] = from_f32<TC>(g / (1.0f + expf(-g)) * u);
+          for (int i = 0; i < 16; i += 4) {
+            float4 f;
+            float* fp = reinterpret_cast<float*>(&f);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const float g = __uint_as_float(v[i + e]), u = __uint_as_float(v[16 + i + e]);
+              fp[e] = g / (1.0f + expf(-g)) * u;
+            }
+            *reinterpret_cast<float4*>(mine + i) = f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(mine + i) = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+        }
+        __syncwarp();
+        const int col = (epilogue == 2 ? ((n0 + c0) >> 1) : (n0 + c0)) + lc;
+        for (int rr = lr; rr < 32; rr += rpp) {
+          const int row = row_base + rr;
+          if (row >= M || col >= n_out) continue;
+          float4 f = *reinterpret_cast<const float4*>(stg + rr * 36 + lc);
+          TC* o = C + (size_t)row * ldc + col;
+          if (vec && col + 3 < n_out) {
+            if (sizeof(TC) == 4) {
+              float4* o4 = reinterpret_cast<float4*>(o);
+              if (epilogue == 1) {
+                const float4 old = *o4;
+                f.x += old.x; f.y += old.y; f.z += old.z; f.w += old.w;
               }
+              *o4 = f;
+            } else {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+              uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              *reinterpret_cast<uint2*>(o) = pk;
             }
           } else {
-            TC* o = C + (size_t)row * ldc + n0 + c0;
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-              if (n0 + c0 + i < N) {
-                float a = __uint_as_float(v[i]);
-                if (epilogue == 1) a += to_f32(o[i]);
-                o[i] = from_f32<TC>(a);
-              }
+            const float* fp = reinterpret_cast<const float*>(&f);
+            for (int e = 0; e < 4 && col + e < n_out; e++) {
+              float a = fp[e];
+              if (epilogue == 1) a += to_f32(o[e]);
+              o[e] = from_f32<TC>(a);
             }
           }
         }
+        __syncwarp();
       }
     }
   }
@@ -322,17 +357,18 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
   LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_tc: adding needs a float C");
   LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_tc: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
   LEB_REQUIRE(status != nullptr, "leb_gemm_bf16_tc: a status word is required");
-  const int BN = N > 128 ? 256 : 128;
+  const long tiles_wide = (long)ceil_div(M, TC_BM) * ceil_div(N, 256);
+  const int BN = (N > 128 && tiles_wide >= 2 * 148) ? 256 : 128;
   CUtensorMap ma, mw;
   if (tensor_map(&ma, A, M, K, lda, TC_BM)) return 1;
   if (tensor_map(&mw, W, N, K, K, BN)) return 1;
   if (c_dtype == LEB_BF16) {
     if (BN == 256) return launch_tc<bf16, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<bf16, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<bf16, 128, 3>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   if (c_dtype == LEB_F32) {
     if (BN == 256) return launch_tc<float, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<float, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<float, 128, 3>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   return leb_fail("leb_gemm_bf16_tc: unknown C dtype %d", c_dtype);
 }
