@@ -282,3 +282,51 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
   LEB_CHECK_LAUNCH("leb_attention_decode");
   return 0;
 }
+
+// ---- the same step for callers that cannot allocate (see leb_no_alloc.h) ---------------------------
+#include "leb_no_alloc.h"
+
+extern "C" int leb_attention_merge(void* out, const float* part, int dtype, const void* gate, int gate_stride,
+                                   int M, int nh, int hd, int n_splits, cudaStream_t st);
+
+// The split partial results of leb_attention_decode_static.  In host code this name is only a
+// handle for cudaGetSymbolAddress, not a device address.
+static __device__ __align__(256) float g_static_scratch[LEB_NO_ALLOC_SCRATCH_FLOATS];
+
+#define LEB_MAX_DEVICES 64
+static float* g_static_scratch_ptr[LEB_MAX_DEVICES];   // device address of the array, per device
+
+LEB_API int leb_attention_decode_static(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                        const int* block_table, int bt_width, const int* seq_slot,
+                                        const int* seq_pos0, const int* seq_qstart, const void* gate,
+                                        int gate_stride, int B, int nh, int nkv, int hd, int page_size,
+                                        int window, float scale, int n_splits, cudaStream_t st) {
+  if (B <= 0) return 0;
+  LEB_REQUIRE(n_splits >= 1, "leb_attention_decode_static: n_splits must be at least 1");
+  float* scratch = nullptr;
+  if (n_splits > 1) {
+    const unsigned long long need = (unsigned long long)B * nh * n_splits * (hd + 2);
+    LEB_REQUIRE(need <= LEB_NO_ALLOC_SCRATCH_FLOATS,
+                "leb_attention_decode_static: %d rows x %d heads x %d splits x (head_dim %d + 2) = %llu floats of "
+                "scratch, the built-in array holds %u; use fewer splits or leb_attention_decode with your own scratch",
+                B, nh, n_splits, hd, need, (unsigned)LEB_NO_ALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return leb_fail("leb_attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    LEB_REQUIRE(dev >= 0 && dev < LEB_MAX_DEVICES, "leb_attention_decode_static: device index %d not taken", dev);
+    if (!g_static_scratch_ptr[dev]) {   // first call on this device (outside any stream capture)
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p)
+        return leb_fail("leb_attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      g_static_scratch_ptr[dev] = (float*)p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  int rc = leb_attention_decode(out, scratch, q, k_pool, v_pool, block_table, bt_width, seq_slot, seq_pos0,
+                                seq_qstart, gate, gate_stride, B, nh, nkv, hd, page_size, window, scale, n_splits, st);
+  if (rc) return rc;
+  if (n_splits > 1)
+    return leb_attention_merge(out, scratch, LEB_BF16, gate, gate_stride, B, nh, hd, n_splits, st);
+  return 0;
+}
