@@ -195,6 +195,9 @@ def time_e2e(eng, batch: int, context: int, steps: int, rng) -> dict:
     """The same decode through Engine.generate: host ids in, host ids out, every step."""
     from lastengine_b200 import SamplingParams
     prompts = [rng.integers(0, eng.vocab_size, size=context - steps - 1).tolist() for _ in range(batch)]
+    # a short call first: it captures the decode graph of this batch size, as a server's first request would
+    eng.generate([p[:64] for p in prompts], SamplingParams(temperature=0.0), max_new_tokens=4, stop_token_ids=[],
+                 max_batch=batch, max_seq_len=context + 1)
     res = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=steps + 1, stop_token_ids=[],
                        max_batch=batch, max_seq_len=context + 1)
     st = res.stats
@@ -215,6 +218,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--only-prefill", action="store_true", help="time the prompt step only (for profiling)")
+    ap.add_argument("--only-decode", action="store_true", help="skip the prompt timing (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -250,7 +254,7 @@ def main() -> int:
     clocks = ClockSampler()
     clocks.start()
     # ---- prefill ---------------------------------------------------------------------------
-    pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
+    pre_ms = time_prefill(eng, PREFILL_TOKENS, 0 if args.only_decode else 3, 1 if args.only_decode else 5, rng)
     pre_flops = (PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"]
                  + nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
     prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,

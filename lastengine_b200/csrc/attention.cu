@@ -192,6 +192,7 @@ template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
                                        const T* __restrict__ gate, int gate_stride, int nh, int hd,
                                        int n_splits) {
+  pdl_wait();
   const size_t m = blockIdx.x;
   const int h = blockIdx.y;
   const float* pp = part + ((m * nh + h) * n_splits) * (size_t)(hd + 2);
@@ -303,7 +304,7 @@ LEB_API int leb_attention_merge(void* out, const float* part, int dtype, const v
   if (dtype == LEB_F32)
     attention_merge_kernel<float><<<grid, 64, 0, st>>>((float*)out, part, (const float*)gate, gate_stride, nh, hd, n_splits);
   else if (dtype == LEB_BF16)
-    attention_merge_kernel<bf16><<<grid, 64, 0, st>>>((bf16*)out, part, (const bf16*)gate, gate_stride, nh, hd, n_splits);
+    leb_launch(attention_merge_kernel<bf16>, grid, dim3(64), 0, st, (bf16*)out, part, (const bf16*)gate, gate_stride, nh, hd, n_splits);
   else
     return leb_fail("leb_attention_merge: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_attention_merge");

@@ -65,6 +65,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
   __shared__ float o_s[ATD_WARPS][16][HD + 4];
   __shared__ float m_s[ATD_WARPS][16], l_s[ATD_WARPS][16];
 
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, c = lane & 3;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -268,7 +269,7 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
   dim3 grid(nkv, B, n_splits);
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_decode: grid too large");
 #define LEB_ATD(HD_)                                                                              \
-  attention_decode_kernel<HD_><<<grid, 32 * ATD_WARPS, 0, st>>>(                                  \
+  leb_launch(attention_decode_kernel<HD_>, grid, dim3(32 * ATD_WARPS), 0, st,                     \
       (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,    \
       bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
       window, scale, n_splits)

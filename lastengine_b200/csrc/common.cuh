@@ -26,6 +26,34 @@ extern long long g_leb_launches;
     g_leb_launches++;                                                                 \
   } while (0)
 
+// Launch with programmatic dependent launch: the kernel may be scheduled while the one before
+// it on the stream is still running, so its start-up (and whatever it does before pdl_wait())
+// overlaps the tail of its predecessor.  A decode step is a chain of ~100 short kernels; this
+// takes the launch gap out of every link.  Kernels launched this way call pdl_wait() before they
+// touch anything the previous kernel wrote, and write nothing before it.
+extern int g_leb_pdl;   // 1: use the attribute (default), 0: plain launches
+template <typename... KArgs, typename... Args>
+static inline cudaError_t leb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_leb_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+// Device side: wait until the previous kernel on the stream has completed and its writes are
+// visible (a no-op for a plain launch), then let the next kernel start its own start-up.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 #define LEB_REQUIRE(cond, ...)                 \
   do {                                         \
     if (!(cond)) return leb_fail(__VA_ARGS__); \

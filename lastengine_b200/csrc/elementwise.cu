@@ -17,6 +17,8 @@ int leb_fail(const char* fmt, ...) {
 LEB_API const char* leb_last_error() { return g_err; }
 
 long long g_leb_launches = 0;
+int g_leb_pdl = 1;
+LEB_API void leb_set_pdl(int on) { g_leb_pdl = on ? 1 : 0; }
 LEB_API long long leb_launch_count() { return g_leb_launches; }
 
 // ---------------------------------------------------------------------------------------------
@@ -24,6 +26,7 @@ LEB_API long long leb_launch_count() { return g_leb_launches; }
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
                              const int* __restrict__ tokens, int D, int V) {
+  pdl_wait();
   int m = blockIdx.x;
   int tok = tokens[m];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);  // ids are validated on the host; never read outside
@@ -37,9 +40,9 @@ LEB_API int leb_embed(float* x, const void* table, int table_dtype, const int* t
   if (M <= 0) return 0;
   int threads = D >= 1024 ? 256 : 128;
   if (table_dtype == LEB_F32)
-    embed_kernel<float><<<M, threads, 0, st>>>(x, (const float*)table, tokens, D, V);
+    leb_launch(embed_kernel<float>, dim3(M), dim3(threads), 0, st, x, (const float*)table, tokens, D, V);
   else if (table_dtype == LEB_BF16)
-    embed_kernel<bf16><<<M, threads, 0, st>>>(x, (const bf16*)table, tokens, D, V);
+    leb_launch(embed_kernel<bf16>, dim3(M), dim3(threads), 0, st, x, (const bf16*)table, tokens, D, V);
   else
     return leb_fail("leb_embed: unknown table dtype %d", table_dtype);
   LEB_CHECK_LAUNCH("leb_embed");
@@ -56,6 +59,7 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
                                const float* __restrict__ w, const int* __restrict__ rows, int D,
                                float eps) {
   __shared__ float red[33];
+  pdl_wait();
   int m = blockIdx.x;
   const float* xi = x + (size_t)(rows ? rows[m] : m) * D;
   float s = 0.f;
@@ -81,11 +85,11 @@ LEB_API int leb_rmsnorm(void* out, int out_dtype, const float* x, const float* w
   int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
   if (add) {
     LEB_REQUIRE(out_dtype == LEB_F32, "leb_rmsnorm: the added form writes the float residual");
-    rmsnorm_kernel<float, true><<<M, threads, 0, st>>>((float*)out, x, w, rows, D, eps);
+    leb_launch(rmsnorm_kernel<float, true>, dim3(M), dim3(threads), 0, st, (float*)out, x, w, rows, D, eps);
   } else if (out_dtype == LEB_F32) {
-    rmsnorm_kernel<float, false><<<M, threads, 0, st>>>((float*)out, x, w, rows, D, eps);
+    leb_launch(rmsnorm_kernel<float, false>, dim3(M), dim3(threads), 0, st, (float*)out, x, w, rows, D, eps);
   } else if (out_dtype == LEB_BF16) {
-    rmsnorm_kernel<bf16, false><<<M, threads, 0, st>>>((bf16*)out, x, w, rows, D, eps);
+    leb_launch(rmsnorm_kernel<bf16, false>, dim3(M), dim3(threads), 0, st, (bf16*)out, x, w, rows, D, eps);
   } else {
     return leb_fail("leb_rmsnorm: unknown output dtype %d", out_dtype);
   }

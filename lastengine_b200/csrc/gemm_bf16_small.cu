@@ -24,7 +24,7 @@
 
 __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -38,6 +38,21 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
                        const int* __restrict__ group_offsets, size_t w_group_stride) {
   __shared__ float red[SM_WARPS][NSUB][SM_ROWS][8 * MT + 1];
   int row_begin = 0, row_end = M;
+  const int n0 = blockIdx.x * (SM_ROWS * NSUB);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!group_offsets) {
+    // The weights do not depend on the kernel before this one: ask for this block's rows to be
+    // brought into L2 now, while that kernel finishes, and only then wait for the activations.
+    const size_t bytes = (size_t)K * 2;
+    for (int rr = 0; rr < SM_ROWS * NSUB; rr++) {
+      const int n = n0 + rr;
+      if (n >= N) break;
+      const char* p = (const char*)(W + (size_t)n * K);
+      for (size_t off = (size_t)threadIdx.x * 128; off < bytes; off += (size_t)blockDim.x * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
+    }
+  }
+  pdl_wait();
   if (group_offsets) {
     row_begin = group_offsets[blockIdx.z];
     row_end = group_offsets[blockIdx.z + 1];
@@ -45,8 +60,6 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
   }
   const int m0 = row_begin + blockIdx.y * (8 * MT);
   if (m0 >= row_end) return;
-  const int n0 = blockIdx.x * (SM_ROWS * NSUB);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, c = lane & 3;
 
   float acc[NSUB][MT][4];
@@ -72,26 +85,33 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
   }
 
   const int n_kb = (K + 31) / 32;
-#pragma unroll 2
-  for (int kb = warp; kb < n_kb; kb += SM_WARPS) {
-    const int k = kb * 32 + c * 8;
-    const bool kin = k < K;  // K is a multiple of 8: a 16-byte piece is inside or outside as a whole
-    uint4 wa[NSUB][2], xb[MT];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
+  // The stream is only as fast as the bytes in flight: a warp first issues the loads of U of
+  // its k-slices (U * (2 NSUB + MT) 16-byte loads per lane), and only then multiplies.
+  constexpr int U = (NSUB * MT <= 1) ? 8 : (NSUB * MT <= 2 ? 4 : (MT <= 4 ? 2 : 1));
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int kb0 = warp; kb0 < n_kb; kb0 += SM_WARPS * U) {
+    uint4 wa[U][NSUB][2], xb[U][MT];
 #pragma unroll
-    for (int s = 0; s < NSUB; s++) {
-      wa[s][0] = kin ? *(const uint4*)(wrow[s][0] + k) : zero;
-      wa[s][1] = kin ? *(const uint4*)(wrow[s][1] + k) : zero;
+    for (int u = 0; u < U; u++) {
+      const int k = (kb0 + u * SM_WARPS) * 32 + c * 8;
+      const bool kin = k < K;  // K is a multiple of 8: a 16-byte piece is inside or outside as a whole
+#pragma unroll
+      for (int s = 0; s < NSUB; s++) {
+        wa[u][s][0] = kin ? __ldg((const uint4*)(wrow[s][0] + k)) : zero;
+        wa[u][s][1] = kin ? __ldg((const uint4*)(wrow[s][1] + k)) : zero;
+      }
+#pragma unroll
+      for (int t = 0; t < MT; t++) xb[u][t] = (kin && arow[t]) ? *(const uint4*)(arow[t] + k) : zero;
     }
 #pragma unroll
-    for (int t = 0; t < MT; t++) xb[t] = (kin && arow[t]) ? *(const uint4*)(arow[t] + k) : zero;
+    for (int u = 0; u < U; u++)
 #pragma unroll
-    for (int s = 0; s < NSUB; s++)
+      for (int s = 0; s < NSUB; s++)
 #pragma unroll
-      for (int t = 0; t < MT; t++) {
-        mma_bf16_16816(acc[s][t], wa[s][0].x, wa[s][1].x, wa[s][0].y, wa[s][1].y, xb[t].x, xb[t].y);
-        mma_bf16_16816(acc[s][t], wa[s][0].z, wa[s][1].z, wa[s][0].w, wa[s][1].w, xb[t].z, xb[t].w);
-      }
+        for (int t = 0; t < MT; t++) {
+          mma_bf16_16816(acc[s][t], wa[u][s][0].x, wa[u][s][1].x, wa[u][s][0].y, wa[u][s][1].y, xb[u][t].x, xb[u][t].y);
+          mma_bf16_16816(acc[s][t], wa[u][s][0].z, wa[u][s][1].z, wa[u][s][0].w, wa[u][s][1].w, xb[u][t].z, xb[u][t].w);
+        }
   }
 
   // accumulator fragment: [0] (row r, col 2c) [1] (r, 2c+1) [2] (r+8, 2c) [3] (r+8, 2c+1)
@@ -147,8 +167,8 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
   if (grid.y > 65535 || grid.z > 65535) return leb_fail("leb_gemm_bf16_small: grid too large");
   dim3 block(32 * SM_WARPS);
 #define LEB_SM(MT_)                                                                          \
-  gemm_bf16_small_kernel<TC, MT_, NSUB><<<grid, block, 0, st>>>((TC*)C, A, W, M, N, K, lda, ldc, \
-                                                                epilogue, group_offsets, w_group_stride)
+  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, ldc, \
+             epilogue, group_offsets, w_group_stride)
   switch (mt) {
     case 1: LEB_SM(1); break;
     case 2: LEB_SM(2); break;

@@ -26,6 +26,7 @@ __global__ void qk_rope_store_kernel(
     const float* __restrict__ inv_freq, int rope_dim, int neox, int nh, int nkv, int hd,
     int page_size) {
   extern __shared__ float sm[];  // one head vector per warp
+  pdl_wait();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   int m = blockIdx.x;
   int head = blockIdx.y * nwarps + warp;  // [0,nh): q; [nh,nh+nkv): k; [nh+nkv, nh+2nkv): v
@@ -112,12 +113,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
   dim3 grid(M, ceil_div(total, nwarps)), block(32 * nwarps);
   size_t smem = (size_t)nwarps * hd * sizeof(float);
   if (dtype == LEB_F32)
-    qk_rope_store_kernel<float, float><<<grid, block, smem, st>>>(
+    leb_launch(qk_rope_store_kernel<float, float>, grid, block, smem, st,
         (float*)q_out, (const float*)q_in, q_stride, (const float*)k_in, (const float*)v_in,
         kv_stride, (float*)k_pool, (float*)v_pool, block_table, bt_width, row_seq, row_pos,
         seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, nh, nkv, hd, page_size);
   else if (dtype == LEB_BF16)
-    qk_rope_store_kernel<bf16, bf16><<<grid, block, smem, st>>>(
+    leb_launch(qk_rope_store_kernel<bf16, bf16>, grid, block, smem, st,
         (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
         (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
         k_norm_w, eps, inv_freq, rope_dim, neox, nh, nkv, hd, page_size);

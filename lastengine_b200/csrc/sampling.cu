@@ -74,9 +74,58 @@ __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ l
   }
 }
 
+// Large vocabularies: several blocks per row fold their best (value, id) key into one word per
+// row with atomicMax (a maximum does not depend on the order), and a second small kernel turns
+// the keys into ids and clears the words for the next call.  The words live in the library
+// (zero when it is loaded, zero again after every call).
+#define ARGMAX_ROWS 4096
+static __device__ unsigned long long g_argmax_best[ARGMAX_ROWS];
+
+__global__ void argmax_part_kernel(const float* __restrict__ logits, int V, int per_block) {
+  __shared__ unsigned long long best[8];
+  pdl_wait();
+  const float* l = logits + (size_t)blockIdx.x * V;
+  const int lo = blockIdx.y * per_block, hi = min(V, lo + per_block);
+  unsigned long long k = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    unsigned long long c = order_key(l[i], i);
+    k = c > k ? c : k;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long c = __shfl_xor_sync(0xffffffffu, k, o);
+    k = c > k ? c : k;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) best[warp] = k;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) k = best[w] > k ? best[w] : k;
+    atomicMax(&g_argmax_best[blockIdx.x], k);
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ out, int n) {
+  pdl_wait();
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = (int)(0xffffffffu - (unsigned)(g_argmax_best[i] & 0xffffffffull));
+  g_argmax_best[i] = 0ull;
+}
+
 LEB_API int leb_argmax(int* out, const float* logits, int n, int V, cudaStream_t st) {
   if (n <= 0) return 0;
   LEB_REQUIRE(V >= 1, "leb_argmax: empty vocabulary");
+  if (V >= 8192 && n <= ARGMAX_ROWS) {
+    const int per_block = 2048;
+    dim3 grid(n, ceil_div(V, per_block));
+    if (grid.y <= 65535) {
+      leb_launch(argmax_part_kernel, grid, dim3(256), 0, st, logits, V, per_block);
+      LEB_CHECK_LAUNCH("leb_argmax");
+      leb_launch(argmax_final_kernel, dim3(ceil_div(n, 128)), dim3(128), 0, st, out, n);
+      LEB_CHECK_LAUNCH("leb_argmax");
+      return 0;
+    }
+  }
   argmax_kernel<<<n, 512, 0, st>>>(out, logits, V);
   LEB_CHECK_LAUNCH("leb_argmax");
   return 0;
@@ -201,6 +250,7 @@ LEB_API int leb_sample(int* out, const float* logits, const float* u01, int n, i
 __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_pos,
                                int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
                                const int* __restrict__ chosen, int B) {
+  pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B || seq_slot[b] < 0) return;
   tokens[b] = chosen[b];
@@ -211,7 +261,7 @@ __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_p
 LEB_API int leb_advance(int* tokens, int* row_pos, int* seq_pos0, const int* seq_slot,
                         const int* chosen, int B, cudaStream_t st) {
   if (B <= 0) return 0;
-  advance_kernel<<<ceil_div(B, 128), 128, 0, st>>>(tokens, row_pos, seq_pos0, seq_slot, chosen, B);
+  leb_launch(advance_kernel, dim3(ceil_div(B, 128)), dim3(128), 0, st, tokens, row_pos, seq_pos0, seq_slot, chosen, B);
   LEB_CHECK_LAUNCH("leb_advance");
   return 0;
 }

@@ -79,6 +79,40 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
   for (int k = 0; k < Lc - 1; k++) sc[k] = nv[k];
 }
 
+// Decode: every sequence brings exactly one row, so one thread per (sequence, channel) reads the
+// state, gives the output and shifts the state, as the reference's one-token kernel does
+// (src/cuda/dense.cu:124-132); one launch instead of two.
+template <typename T>
+__global__ void shortconv_single_kernel(T* __restrict__ y, const T* __restrict__ bcx,
+                                        const float* __restrict__ w, const float* __restrict__ bias,
+                                        float* __restrict__ state, const int* __restrict__ seq_slot,
+                                        const int* __restrict__ seq_qstart, int D, int Lc) {
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  if (ch >= D) return;
+  const int slot = seq_slot[b];
+  const size_t m = seq_qstart[b];
+  if (slot < 0) {
+    y[m * D + ch] = from_f32<T>(0.f);
+    return;
+  }
+  const T* r = bcx + m * 3 * D;
+  const float bx = to_f32(r[ch]) * to_f32(r[2 * D + ch]);
+  const float* wc = w + (size_t)ch * Lc;
+  float* sc = state + ((size_t)slot * D + ch) * (Lc - 1);
+  float acc = bias ? bias[ch] : 0.f;
+  float s[16];
+  for (int k = 0; k < Lc - 1; k++) {
+    s[k] = sc[k];
+    acc += wc[k] * s[k];       // same order of taps as the row kernel: oldest first
+  }
+  acc += wc[Lc - 1] * bx;
+  for (int k = 0; k < Lc - 2; k++) sc[k] = s[k + 1];
+  sc[Lc - 2] = bx;
+  y[m * D + ch] = from_f32<T>(to_f32(r[D + ch]) * acc);
+}
+
 LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, const float* bias,
                           float* state, const int* row_seq, const int* seq_slot,
                           const int* seq_qstart, const int* seq_qlen, int M, int B, int D, int Lc,
@@ -86,6 +120,17 @@ LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, c
   if (M <= 0 || B <= 0) return 0;
   LEB_REQUIRE(Lc >= 2 && Lc <= 17, "leb_shortconv: conv length %d outside 2..17", Lc);
   dim3 block(128);
+  if (seq_qlen == nullptr) {   // the caller vouches that every sequence has one row
+    dim3 g(B, ceil_div(D, 128));
+    if (dtype == LEB_F32)
+      leb_launch(shortconv_single_kernel<float>, g, block, 0, st, (float*)y, (const float*)bcx, w, bias, state, seq_slot, seq_qstart, D, Lc);
+    else if (dtype == LEB_BF16)
+      leb_launch(shortconv_single_kernel<bf16>, g, block, 0, st, (bf16*)y, (const bf16*)bcx, w, bias, state, seq_slot, seq_qstart, D, Lc);
+    else
+      return leb_fail("leb_shortconv: unknown dtype %d", dtype);
+    LEB_CHECK_LAUNCH("leb_shortconv");
+    return 0;
+  }
   dim3 g1(M, ceil_div(D, 128)), g2(B, ceil_div(D, 128));
   if (dtype == LEB_F32) {
     shortconv_rows_kernel<float><<<g1, block, 0, st>>>((float*)y, (const float*)bcx, w, bias, state,

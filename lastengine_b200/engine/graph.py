@@ -100,9 +100,12 @@ class GraphBackend(EngineBackend):
 
     def __init__(self, engine, sampling: SamplingParams, max_batch: int = 64, max_seq_len: int | None = None):
         super().__init__(engine, sampling)
-        self.graphs: dict[int, DecodeGraph] = {}
         page = engine.cache.page_size
         self.width = -(-(max_seq_len or engine.max_tokens) // page)
+        # Captured graphs outlive one call: they belong to the engine, keyed by what is baked into
+        # them (the sampling constants and the width of the page tables).
+        store = engine.__dict__.setdefault("_decode_graphs", {})
+        self.graphs: dict[int, DecodeGraph] = store.setdefault((sampling, self.width), {})
         self.h2d_bytes = 0
 
     def decode(self, slots, tokens, u01, histories):

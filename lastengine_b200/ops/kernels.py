@@ -172,9 +172,10 @@ def shortconv(y: torch.Tensor, bcx: torch.Tensor, w: torch.Tensor, bias: torch.T
     assert state.shape[1:] == (D, Lc - 1)
     if bias is not None:
         _cuda(bias, "shortconv.bias", torch.float32)
+    single = batch.max_qlen == 1 and M == batch.n_seqs     # decode: the one-launch form
     _check(lib().leb_shortconv(_ptr(y), _ptr(bcx), _dt(y, "shortconv"), _ptr(w), _ptr(bias), _ptr(state),
                                _ptr(batch.row_seq), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
-                               _ptr(batch.seq_qlen), M, batch.n_seqs, D, Lc, _stream()))
+                               None if single else _ptr(batch.seq_qlen), M, batch.n_seqs, D, Lc, _stream()))
 
 
 def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | None,
@@ -219,7 +220,7 @@ def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
     if batch.max_qlen != 1:
         return 1
     per = batch.n_seqs * nkv * ((G + 15) // 16)
-    return max(1, min(32, (2 * sm_count) // max(per, 1)))
+    return max(1, min(32, (4 * sm_count) // max(per, 1)))
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
