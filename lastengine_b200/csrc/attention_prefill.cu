@@ -11,7 +11,9 @@
 //
 // A block owns one sequence, one kv head and QT consecutive positions: QT*G rows, 16*MT per
 // warp.  Every warp walks the key blocks of 32 positions its rows can see, causally and inside
-// the window, with a running (max, sum, acc) per row.  Keys and values come from the cache
+// the window, with a running (max, sum, acc) per row; the fragments of the next block are
+// loaded while the current one is multiplied, exponentials are 2^x on scores pre-multiplied by
+// log2(e), and blocks wholly below the diagonal skip the mask.  Keys and values come from the cache
 // only, which already holds this step's rows.
 #include "common.cuh"
 
@@ -20,7 +22,7 @@
 
 __device__ __forceinline__ void mma16816p(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -127,28 +129,58 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
   }
 
   const int* table = block_table + (size_t)b * bt_width;
-  for (int blk = key_lo / 32; blk <= key_hi / 32; blk++) {
+  // Scores are kept in base 2: s2 = (q.k) * scale * log2(e), p = 2^(s2 - max2) = e^(s - max).
+  const float scale2 = scale * 1.4426950408889634f;
+  // the lowest query position among this lane's rows: blocks wholly at or below it need no mask
+  int qmin = 0x7fffffff;
+#pragma unroll
+  for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) qmin = min(qmin, pos0 + rpos[mt][hh]);
+  qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, 4));
+  qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, 8));
+  qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, 16));
+
+  const int blk_first = key_lo / 32, blk_last = key_hi / 32;
+  uint4 kf[4][KB], vf[NT];      // the block being multiplied
+  uint4 kn[4][KB], vn[NT];      // the next block, in flight meanwhile
+  auto load_block = [&](int blk, uint4 (&kd)[4][KB], uint4 (&vd)[NT]) {
     const int key0 = blk * 32;
     const int page = table[key0 / page_size];
     const int off = key0 % page_size;
     const bf16* kbase = k_pool + (((size_t)page * nkv + kvh) * page_size + off) * HD;
     const bf16* vbase = v_pool + ((size_t)page * nkv + kvh) * HD * page_size + off;
-    uint4 kf[4][KB];
 #pragma unroll
     for (int t = 0; t < 4; t++) {
       const int kp = 8 * (r >> 1) + 2 * t + (r & 1);
 #pragma unroll
       for (int j = 0; j < KB; j++)
-        kf[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
+        kd[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
     }
-    uint4 vf[NT];
 #pragma unroll
     for (int n = 0; n < NT; n++)
-      vf[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+      vd[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+  };
+  constexpr bool PREFETCH = HD <= 64;   // larger heads have no registers to spare for a second block
+  if (PREFETCH) load_block(blk_first, kn, vn);
+  for (int blk = blk_first; blk <= blk_last; blk++) {
+    const int key0 = blk * 32;
+    if (PREFETCH) {
+#pragma unroll
+      for (int t = 0; t < 4; t++)
+#pragma unroll
+        for (int j = 0; j < KB; j++) kf[t][j] = kn[t][j];
+#pragma unroll
+      for (int n = 0; n < NT; n++) vf[n] = vn[n];
+      if (blk < blk_last) load_block(blk + 1, kn, vn);
+    } else {
+      load_block(blk, kf, vf);
+    }
     if (key0 + 32 > kv_len) {
 #pragma unroll
       for (int n = 0; n < NT; n++) vf[n] = mask_tail(vf[n], key0 + 8 * c, kv_len);
     }
+    const bool need_mask = window > 0 || key0 + 31 > qmin;
 
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
@@ -164,24 +196,34 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
         }
       }
       float tmax[2] = {ATP_NEG, ATP_NEG};
+      if (need_mask) {
 #pragma unroll
-      for (int t = 0; t < 4; t++)
+        for (int t = 0; t < 4; t++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int hh = e >> 1;
-          const int kp = key0 + 8 * c + 2 * t + (e & 1);
-          const int qp = pos0 + rpos[mt][hh];
-          const bool valid = kp <= qp && (window <= 0 || kp + window > qp);
-          s[t][e] = valid ? s[t][e] * scale : ATP_NEG;
-          tmax[hh] = fmaxf(tmax[hh], s[t][e]);
-        }
+          for (int e = 0; e < 4; e++) {
+            const int hh = e >> 1;
+            const int kp = key0 + 8 * c + 2 * t + (e & 1);
+            const int qp = pos0 + rpos[mt][hh];
+            const bool valid = kp <= qp && (window <= 0 || kp + window > qp);
+            s[t][e] = valid ? s[t][e] * scale2 : ATP_NEG;
+            tmax[hh] = fmaxf(tmax[hh], s[t][e]);
+          }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            s[t][e] *= scale2;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], s[t][e]);
+          }
+      }
       float corr[2];
 #pragma unroll
       for (int hh = 0; hh < 2; hh++) {
         tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 1));
         tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 2));
         const float mn = fmaxf(mx[mt][hh], tmax[hh]);
-        corr[hh] = expf(mx[mt][hh] - mn);
+        corr[hh] = exp2f(mx[mt][hh] - mn);
         mx[mt][hh] = mn;
       }
       float psum[2] = {0.f, 0.f};
@@ -191,7 +233,8 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
         float p[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-          p[e] = s[t][e] > 0.5f * ATP_NEG ? expf(s[t][e] - mx[mt][e >> 1]) : 0.f;
+          // a masked score is -1e30: 2^(-1e30 - max) is 0 unless the whole row is still masked
+          p[e] = (need_mask && s[t][e] <= 0.5f * ATP_NEG) ? 0.f : exp2f(s[t][e] - mx[mt][e >> 1]);
           psum[e >> 1] += p[e];
         }
         pa[t][0] = pack2(p[0], p[1]);
@@ -249,7 +292,7 @@ LEB_API int leb_attention_prefill(void* out, const void* q, const void* k_pool, 
   LEB_REQUIRE(leb_attention_prefill_supported(nh, nkv, hd, page_size),
               "leb_attention_prefill: sizes not taken (heads %d, kv heads %d, head_dim %d, page %d)", nh, nkv, hd, page_size);
   const int G = nh / nkv;
-  const int MT = hd <= 64 ? 2 : 1;
+  const int MT = hd <= 32 ? 2 : 1;
   const int rows_per_block = ATP_WARPS * MT * 16;
   int QT = rows_per_block / G;
   if (QT < 1) QT = 1;
@@ -262,7 +305,7 @@ LEB_API int leb_attention_prefill(void* out, const void* q, const void* k_pool, 
       window, scale, QT)
   switch (hd) {
     case 32: LEB_ATP(32, 2); break;
-    case 64: LEB_ATP(64, 2); break;
+    case 64: LEB_ATP(64, 1); break;
     case 96: LEB_ATP(96, 1); break;
     default: LEB_ATP(128, 1); break;
   }

@@ -3,7 +3,7 @@
 //
 // The reference multiplies prompt chunks with tiled mma.sync kernels over weights it
 // dequantises into shared memory (src/cuda/kernels.cu:965-1235, tiles 64x64 to 128x128).  Here
-// a block computes one 128 x BN tile:
+// a block works through 128 x BN tiles (one block per SM, tiles dealt out round-robin):
 //   warp 0   one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the A and W
 //            tiles of 64 k-values into a ring of shared-memory stages;
 //   warp 1   allocates tensor memory; one thread issues tcgen05.mma (128 x BN x 16 per
@@ -12,6 +12,8 @@
 //   warps 2-5  wait for the accumulator, read it with tcgen05.ld (32 rows per warp, 32 columns at
 //            a time) and apply the epilogue: store, add into the float residual, or SwiGLU over
 //            gate/up rows interleaved in blocks of 16.
+// Tensor memory holds two accumulators, so the epilogue of one tile runs while the products of
+// the next are issued.
 // Rows and columns beyond M, N and K are zero-filled by TMA and masked in the epilogue, so any
 // M, N and any K that is a multiple of 8 are taken.
 //
@@ -125,26 +127,33 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint8_t* sb = smem + STAGES * A_BYTES;
   uint64_t* full = (uint64_t*)(sb + STAGES * B_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  uint64_t* acc_full = empty + STAGES;      // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* stage_out = (float*)(tmem_slot + 4);   // 4 warps x 32 rows x 36 floats for the epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
   const int nk = (K + TC_BK - 1) / TC_BK;
+  const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;   // tile t: rows (t % m_tiles), columns (t / m_tiles):
+                                             // blocks running together share weight tiles in L2
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);   // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, BN);   // BN columns of 128 lanes x 32 bits: the float accumulator
+    tmem_alloc(tmem_slot, 2 * BN);   // two accumulators of BN columns x 128 lanes x 32 bits
     tmem_relinquish();
   }
   tc_fence_before();
@@ -154,12 +163,17 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nk; kb++) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 1); break; }
-        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-        tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kb * TC_BK, m0);
-        tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+      uint32_t it = 0;   // k-slices loaded so far, over all tiles of this block
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < nk; kb++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 1); ok = false; break; }
+          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+          tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kb * TC_BK, m0);
+          tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -167,18 +181,26 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N, M
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
       bool ok = true;
-      for (int kb = 0; kb < nk && ok; kb++) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag)) { atomicExch(status, 2); ok = false; break; }
+      uint32_t it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, t++) {
+        const uint32_t buf = t & 1;
+        // the epilogue must have emptied this accumulator (two tiles ago)
+        if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) { atomicExch(status, 4); ok = false; break; }
         tc_fence_after();
-        const uint64_t da = make_desc(smem_u32(sa + s * A_BYTES));
-        const uint64_t db = make_desc(smem_u32(sb + s * B_BYTES));
+        const uint32_t d_tmem = tmem_acc + buf * BN;
+        for (int kb = 0; kb < nk; kb++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { atomicExch(status, 2); ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_desc(smem_u32(sa + s * A_BYTES));
+          const uint64_t db = make_desc(smem_u32(sb + s * B_BYTES));
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; k++)   // 16 k-values = 32 bytes along the swizzled row
-          umma_bf16(tmem_acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-        umma_commit(&empty[s]);   // the stage is free once these products have read it
+          for (int k = 0; k < TC_BK / 16; k++)   // 16 k-values = 32 bytes along the swizzled row
+            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);   // the stage is free once these products have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);
       }
-      if (ok) umma_commit(acc_full);
     }
   } else {
     // epilogue warps: tensor-memory lanes 32*(warp%4) .. +31 are rows of the tile
@@ -186,13 +208,18 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // Each warp stages its 32 rows of a 32-column piece in shared memory (the pipeline's first
     // stage, free once the accumulator is complete) and writes them out row by row, so that a
     // store covers whole 128-byte lines instead of one element in each of 32 rows.
-    float* stg = reinterpret_cast<float*>(smem) + quad * (32 * 36);
+    float* stg = stage_out + quad * (32 * 36);
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, t++) {
+    const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+    const uint32_t buf = t & 1;
     const int row_base = m0 + quad * 32;
-    bool ok = mbar_wait(acc_full, 0, abort_flag);
+    bool ok = mbar_wait(&acc_full[buf], (t >> 1) & 1, abort_flag);
     if (!ok && lane == 0) atomicExch(status, 3);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // the warp leaves together
+    if (!ok) break;
     tc_fence_after();
-    if (ok) {
+    {
       const int ncols = epilogue == 2 ? 16 : 32;          // output columns per piece
       const int n_out = epilogue == 2 ? N / 2 : N;
       const int lpr = ncols / 4, rpp = 32 / lpr;          // lanes per row, rows per pass
@@ -201,7 +228,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld32(tmem_acc + ((uint32_t)(quad * 32) << 16) + buf * BN + (uint32_t)c0, v);
         tmem_ld_wait();
         float* mine = stg + lane * 36;
         if (epilogue == 2) {
@@ -225,6 +252,27 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         __syncwarp();
         const int col = (epilogue == 2 ? ((n0 + c0) >> 1) : (n0 + c0)) + lc;
+        if (epilogue == 1 && sizeof(TC) == 4 && vec && col + 3 < n_out) {
+          // adding into the residual: fetch all eight old pieces first, then add and store, so
+          // the eight loads are in flight together instead of one round trip per row
+          float4 old[8];
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const int row = row_base + lr + 4 * it;
+            old[it] = row < M ? __ldcs(reinterpret_cast<const float4*>(C + (size_t)row * ldc + col))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const int rr = lr + 4 * it, row = row_base + rr;
+            if (row >= M) continue;
+            const float4 f = *reinterpret_cast<const float4*>(stg + rr * 36 + lc);
+            *reinterpret_cast<float4*>(C + (size_t)row * ldc + col) =
+                make_float4(f.x + old[it].x, f.y + old[it].y, f.z + old[it].z, f.w + old[it].w);
+          }
+          __syncwarp();
+          continue;
+        }
         for (int rr = lr; rr < 32; rr += rpp) {
           const int row = row_base + rr;
           if (row >= M || col >= n_out) continue;
@@ -255,12 +303,17 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
       }
     }
+    // this warp has read its part of the accumulator: hand the buffer back to the issuing thread
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, BN);
+    tmem_dealloc(tmem_acc, 2 * BN);
   }
 }
 
@@ -327,7 +380,8 @@ static int tensor_map(CUtensorMap* out, const void* ptr, int rows, int cols, int
 template <typename TC, int BN, int STAGES>
 static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, int ldc,
                      int epilogue, int* status, cudaStream_t st) {
-  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 +
+                          4 * 32 * 36 * 4 + 1024;
   auto kern = gemm_bf16_tc_kernel<TC, BN, STAGES>;
   static bool set = false;
   if (!set) {
@@ -335,8 +389,14 @@ static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int 
     if (e != cudaSuccess) return leb_fail("leb_gemm_bf16_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     set = true;
   }
-  dim3 grid(ceil_div(N, BN), ceil_div(M, TC_BM));
-  if (grid.y > 65535) return leb_fail("leb_gemm_bf16_tc: too many rows (%d)", M);
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+  }
+  const long tiles = (long)ceil_div(N, BN) * ceil_div(M, TC_BM);
+  dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));
   kern<<<grid, TC_THREADS, smem, st>>>(ma, mw, (TC*)C, M, N, K, ldc, epilogue, status);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_tc");
   return 0;
@@ -357,18 +417,19 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
   LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_tc: adding needs a float C");
   LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_tc: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
   LEB_REQUIRE(status != nullptr, "leb_gemm_bf16_tc: a status word is required");
+  // wide tiles read less per flop; narrow ones spread a small product over more SMs
   const long tiles_wide = (long)ceil_div(M, TC_BM) * ceil_div(N, 256);
-  const int BN = (N > 128 && tiles_wide >= 2 * 148) ? 256 : 128;
+  const int BN = (N > 128 && tiles_wide >= 64) ? 256 : 128;
   CUtensorMap ma, mw;
   if (tensor_map(&ma, A, M, K, lda, TC_BM)) return 1;
   if (tensor_map(&mw, W, N, K, K, BN)) return 1;
   if (c_dtype == LEB_BF16) {
     if (BN == 256) return launch_tc<bf16, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<bf16, 128, 3>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<bf16, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   if (c_dtype == LEB_F32) {
     if (BN == 256) return launch_tc<float, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<float, 128, 3>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<float, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   return leb_fail("leb_gemm_bf16_tc: unknown C dtype %d", c_dtype);
 }

@@ -51,6 +51,61 @@ __global__ void shortconv_rows_kernel(T* __restrict__ y, const T* __restrict__ b
   yo[ch] = from_f32<T>(to_f32(r[D + ch]) * acc);
 }
 
+// The same for bfloat16 rows with 16-byte loads: a thread owns 8 channels of one row.
+__global__ void shortconv_rows_bf16x8_kernel(bf16* __restrict__ y, const bf16* __restrict__ bcx,
+                                             const float* __restrict__ w, const float* __restrict__ bias,
+                                             const float* __restrict__ state, const int* __restrict__ row_seq,
+                                             const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                                             int D, int Lc) {
+  const int m = blockIdx.x;
+  const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (ch0 >= D) return;
+  const int b = row_seq[m];
+  const int slot = seq_slot[b];
+  uint4* yo = reinterpret_cast<uint4*>(y + (size_t)m * D + ch0);
+  if (slot < 0) {
+    *yo = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int i = m - seq_qstart[b];
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) acc[e] = bias ? bias[ch0 + e] : 0.f;
+  for (int j = 0; j < Lc; j++) {
+    const int src = i - (Lc - 1) + j;
+    float bx[8];
+    if (src >= 0) {
+      const bf16* r = bcx + (size_t)(m - i + src) * 3 * D;
+      const uint4 Bv = *reinterpret_cast<const uint4*>(r + ch0);
+      const uint4 Xv = *reinterpret_cast<const uint4*>(r + 2 * D + ch0);
+      const __nv_bfloat162* Bp = reinterpret_cast<const __nv_bfloat162*>(&Bv);
+      const __nv_bfloat162* Xp = reinterpret_cast<const __nv_bfloat162*>(&Xv);
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float2 bf = __bfloat1622float2(Bp[e]), xf = __bfloat1622float2(Xp[e]);
+        bx[2 * e] = bf.x * xf.x;
+        bx[2 * e + 1] = bf.y * xf.y;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) bx[e] = state[((size_t)slot * D + ch0 + e) * (Lc - 1) + (Lc - 1) + src];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[e] += w[(size_t)(ch0 + e) * Lc + j] * bx[e];
+  }
+  const uint4 Cv = *reinterpret_cast<const uint4*>(bcx + (size_t)m * 3 * D + D + ch0);
+  const __nv_bfloat162* Cp = reinterpret_cast<const __nv_bfloat162*>(&Cv);
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const float2 cf = __bfloat1622float2(Cp[e]);
+    __nv_bfloat162 v = __floats2bfloat162_rn(cf.x * acc[2 * e], cf.y * acc[2 * e + 1]);
+    op[e] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  *yo = o;
+}
+
 // New state of each sequence: the last Lc-1 values of (old state ++ bx of this step's rows).
 template <typename T>
 __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
@@ -138,8 +193,12 @@ LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, c
     shortconv_state_kernel<float><<<g2, block, 0, st>>>((const float*)bcx, state, seq_slot,
                                                         seq_qstart, seq_qlen, D, Lc);
   } else if (dtype == LEB_BF16) {
-    shortconv_rows_kernel<bf16><<<g1, block, 0, st>>>((bf16*)y, (const bf16*)bcx, w, bias, state,
-                                                      row_seq, seq_slot, seq_qstart, D, Lc);
+    if (D % 8 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)bcx % 16) == 0)
+      shortconv_rows_bf16x8_kernel<<<dim3(M, ceil_div(D / 8, 128)), block, 0, st>>>(
+          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, D, Lc);
+    else
+      shortconv_rows_kernel<bf16><<<g1, block, 0, st>>>((bf16*)y, (const bf16*)bcx, w, bias, state,
+                                                        row_seq, seq_slot, seq_qstart, D, Lc);
     shortconv_state_kernel<bf16><<<g2, block, 0, st>>>((const bf16*)bcx, state, seq_slot,
                                                        seq_qstart, seq_qlen, D, Lc);
   } else {

@@ -53,7 +53,7 @@ def test_rmsnorm(D):
     assert err(out, want) < 1e-6
     ob = torch.empty(7, D, device=DEV, dtype=torch.bfloat16)
     K().rmsnorm(ob, x.to(DEV), w.to(DEV), 1e-3)
-    assert torch.equal(ob.cpu(), out.cpu().to(torch.bfloat16))
+    assert err(ob, want) < 5e-3                     # its own order of sums: equal up to one bfloat16 rounding
     rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
     o3 = torch.empty(3, D, device=DEV)
     K().rmsnorm(o3, x.to(DEV), w.to(DEV), 1e-3, rows=rows)
