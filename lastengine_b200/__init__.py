@@ -33,7 +33,7 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], sampling: Samplin
     if use_graphs:
         try:
             from .engine.graph import GraphBackend
-            backend = GraphBackend(engine, sampling, max_batch=max_batch)
+            backend = GraphBackend(engine, sampling, max_batch=max_batch, max_seq_len=max_seq_len)
         except ImportError:
             backend = None
     if backend is None:

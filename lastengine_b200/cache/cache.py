@@ -108,6 +108,7 @@ class Cache:
         self.dtype, self.device = dtype, device
         self.slots = IdPool(self.max_seqs, "sequence slot")
         self.lens: dict[int, int] = {}
+        self.state_version = 0      # bumped by every change of lengths, pages or slots
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
         self._where: dict[int, tuple[str, int]] = {}
@@ -130,6 +131,7 @@ class Cache:
     # ---- sequences -----------------------------------------------------------------------
     def alloc_seq(self) -> int:
         slot = self.slots.alloc()
+        self.state_version += 1
         self.lens[slot] = 0
         for g in self.state_groups:
             g.data[:, slot].zero_()
@@ -138,6 +140,7 @@ class Cache:
     def free_seq(self, slot: int) -> None:
         if not self.slots.holds(slot):
             raise CacheError(f"sequence slot {slot} is not held (freed twice, or never given out)")
+        self.state_version += 1
         for g in self.kv_groups:
             g.release(slot)
         del self.lens[slot]
@@ -163,6 +166,7 @@ class Cache:
 
     def commit(self, grow: dict[int, int]) -> None:
         """After the step ran: the sequences are `grow[slot]` positions longer."""
+        self.state_version += 1
         for s, n in grow.items():
             self.lens[s] += n
             for g in self.kv_groups:

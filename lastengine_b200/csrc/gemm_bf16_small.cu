@@ -31,7 +31,8 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <typename TC, int MT, int NSUB>  // MT tiles of 8 activation rows, NSUB tiles of 16 weight rows
+// MT tiles of 8 activation rows, NSUB tiles of 16 weight rows, U k-slices of a warp loaded at once
+template <typename TC, int MT, int NSUB, int U>
 __global__ void __launch_bounds__(32 * SM_WARPS)
 gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
                        int M, int N, int K, int lda, int ldc, int epilogue,
@@ -86,8 +87,9 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
 
   const int n_kb = (K + 31) / 32;
   // The stream is only as fast as the bytes in flight: a warp first issues the loads of U of
-  // its k-slices (U * (2 NSUB + MT) 16-byte loads per lane), and only then multiplies.
-  constexpr int U = (NSUB * MT <= 1) ? 8 : (NSUB * MT <= 2 ? 4 : (MT <= 4 ? 2 : 1));
+  // its k-slices (U * (2 NSUB + MT) 16-byte loads per lane), and only then multiplies.  A deep
+  // U costs registers, hence resident blocks: the launcher picks the deepest U whose blocks
+  // still all fit on the GPU at once (a second, partial wave would double the time).
   const uint4 zero = make_uint4(0, 0, 0, 0);
   for (int kb0 = warp; kb0 < n_kb; kb0 += SM_WARPS * U) {
     uint4 wa[U][NSUB][2], xb[U][MT];
@@ -166,15 +168,32 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
   dim3 grid(ceil_div(N, SM_ROWS * NSUB), ceil_div(rows_hint, 8 * mt), group_offsets ? n_groups : 1);
   if (grid.y > 65535 || grid.z > 65535) return leb_fail("leb_gemm_bf16_small: grid too large");
   dim3 block(32 * SM_WARPS);
-#define LEB_SM(MT_)                                                                          \
-  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, ldc, \
+#define LEB_SM(MT_, U_)                                                                          \
+  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB, U_>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, ldc, \
              epilogue, group_offsets, w_group_stride)
   switch (mt) {
-    case 1: LEB_SM(1); break;
-    case 2: LEB_SM(2); break;
-    case 4: LEB_SM(4); break;
+    case 1: {
+      // blocks resident per SM for each depth (asked once), and the SM count
+      static int occ[3] = {0, 0, 0}, n_sm = 0;
+      if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[0], gemm_bf16_small_kernel<TC, 1, NSUB, 8>, 32 * SM_WARPS, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[1], gemm_bf16_small_kernel<TC, 1, NSUB, 4>, 32 * SM_WARPS, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[2], gemm_bf16_small_kernel<TC, 1, NSUB, 2>, 32 * SM_WARPS, 0);
+        if (n_sm <= 0) n_sm = 148;
+      }
+      const long blocks = (long)grid.x * grid.y * grid.z;
+      if (blocks <= (long)occ[0] * n_sm || blocks > 4L * occ[2] * n_sm) LEB_SM(1, 8);   // one wave, or many
+      else if (blocks <= (long)occ[1] * n_sm) LEB_SM(1, 4);
+      else LEB_SM(1, 2);
+      break;
+    }
+    case 2: LEB_SM(2, 2); break;
+    case 4: LEB_SM(4, (NSUB == 1 ? 2 : 1)); break;
     default:
-      if constexpr (NSUB == 1) LEB_SM(8);
+      if constexpr (NSUB == 1) LEB_SM(8, 1);
       break;
   }
 #undef LEB_SM

@@ -4,8 +4,10 @@
 // The reference multiplies prompt chunks with tiled mma.sync kernels over weights it
 // dequantises into shared memory (src/cuda/kernels.cu:965-1235, tiles 64x64 to 128x128).  Here
 // a block works through 128 x BN tiles (one block per SM, tiles dealt out round-robin):
-//   warp 0   one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the A and W
-//            tiles of 64 k-values into a ring of shared-memory stages;
+//   warps 0, 6  one thread each issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+//            A tiles (warp 0) and the W tiles (warp 6) of 64 k-values into a ring of shared-memory
+//            stages; issuing a TMA load costs its thread some hundred cycles, so two threads
+//            keep the ring fuller than one;
 //   warp 1   allocates tensor memory; one thread issues tcgen05.mma (128 x BN x 16 per
 //            instruction, operands from shared memory through descriptors, accumulator in tensor
 //            memory) and commits each stage back to the producer;
@@ -28,7 +30,7 @@
 
 #define TC_BM 128
 #define TC_BK 64
-#define TC_THREADS 192
+#define TC_THREADS 224
 #define TC_SPIN_LIMIT (1u << 22)
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -141,7 +143,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], 2);    // the two producers each announce their bytes
       mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 2; i++) {
@@ -161,8 +163,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
     if (lane == 0) {
+      const bool loads_a = warp == 0;
       uint32_t it = 0;   // k-slices loaded so far, over all tiles of this block
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -170,9 +173,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb = 0; kb < nk; kb++, it++) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 1); ok = false; break; }
-          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-          tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kb * TC_BK, m0);
-          tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+          mbar_expect_tx(&full[s], loads_a ? A_BYTES : B_BYTES);
+          // Tiles that share rows of A start their walk over k at different places, so that
+          // blocks running in step do not all ask L2 for the same lines at the same moment.
+          const int kk = (kb + (tile / m_tiles) * 5) % nk;
+          if (loads_a) tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kk * TC_BK, m0);
+          else tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kk * TC_BK, n0);
         }
       }
     }
@@ -418,18 +424,27 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
   LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_tc: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
   LEB_REQUIRE(status != nullptr, "leb_gemm_bf16_tc: a status word is required");
   // wide tiles read less per flop; narrow ones spread a small product over more SMs
-  const long tiles_wide = (long)ceil_div(M, TC_BM) * ceil_div(N, 256);
-  const int BN = (N > 128 && tiles_wide >= 64) ? 256 : 128;
+  // With few rows (a decode step of some dozens of sequences) the product is bound by reading W:
+  // narrow tiles then give every SM a stripe of W to stream.
+  const long m_tiles = ceil_div(M, TC_BM);
+  int BN = 32;
+  if (N > 128 && m_tiles * ceil_div(N, 256) >= 64) BN = 256;
+  else if (m_tiles * ceil_div(N, 128) >= 96) BN = 128;
+  else if (m_tiles * ceil_div(N, 64) >= 96) BN = 64;
   CUtensorMap ma, mw;
   if (tensor_map(&ma, A, M, K, lda, TC_BM)) return 1;
   if (tensor_map(&mw, W, N, K, K, BN)) return 1;
   if (c_dtype == LEB_BF16) {
     if (BN == 256) return launch_tc<bf16, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<bf16, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    if (BN == 128) return launch_tc<bf16, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    if (BN == 64) return launch_tc<bf16, 64, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<bf16, 32, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   if (c_dtype == LEB_F32) {
     if (BN == 256) return launch_tc<float, 256, 4>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
-    return launch_tc<float, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    if (BN == 128) return launch_tc<float, 128, 6>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    if (BN == 64) return launch_tc<float, 64, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
+    return launch_tc<float, 32, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   return leb_fail("leb_gemm_bf16_tc: unknown C dtype %d", c_dtype);
 }

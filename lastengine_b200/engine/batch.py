@@ -71,9 +71,10 @@ class BatchBuilder:
         lr = np.asarray(logit_rows, dtype=np.int32)
         pieces = [tok, row_seq, row_pos, np.asarray(slots, dtype=np.int32), pos0a, qstart, qlen, lr]
         tkeys = sorted(tables)
-        pieces += [np.ascontiguousarray(tables[k], dtype=np.int32).reshape(-1) for k in tkeys]
         if u01 is not None:
             pieces.append(np.asarray(u01, dtype=np.float32).view(np.int32))
+        n_head = len(pieces)      # the page tables come last: they change least often
+        pieces += [np.ascontiguousarray(tables[k], dtype=np.int32).reshape(-1) for k in tkeys]
         # 4-int alignment keeps every piece 16-byte aligned
         offs, total = [], 0
         for p in pieces:
@@ -91,6 +92,11 @@ class BatchBuilder:
                 self._copied = torch.cuda.Event()
             self._copied.record()
         self.last_h2d_bytes = total * 4
+        names = ["tokens", "row_seq", "row_pos", "seq_slot", "seq_pos0", "seq_qstart", "seq_qlen", "logit_rows"]
+        names += (["u01"] if u01 is not None else []) + [f"table{k}" for k in tkeys]
+        self.layout = {n: (o, p.size) for n, o, p in zip(names, offs, pieces)}
+        self.total = total
+        self.head_total = offs[n_head] if tkeys else total     # everything before the page tables
         d = self._dev
 
         def piece(i):
@@ -98,11 +104,27 @@ class BatchBuilder:
 
         tabs = {}
         for j, k in enumerate(tkeys):
-            tabs[k] = piece(8 + j).view(B, -1)
-        u = piece(8 + len(tkeys)).view(torch.float32) if u01 is not None else None
+            tabs[k] = piece(n_head + j).view(B, -1)
+        u = piece(8).view(torch.float32) if u01 is not None else None
         return StepBatch(
             n_rows=M, n_seqs=B, max_qlen=int(qlen.max()) if B else 0,
             max_kvlen=int((pos0a + qlen).max()) if B else 0,
             tokens=piece(0), row_seq=piece(1), row_pos=piece(2), seq_slot=piece(3), seq_pos0=piece(4),
             seq_qstart=piece(5), seq_qlen=piece(6), logit_rows=piece(7), n_logit_rows=int(lr.size),
             tables=tabs, u01=u, slots_host=list(slots))
+
+    # ---- the same step again, one position later -----------------------------------------------
+    def host_view(self, name: str) -> np.ndarray:
+        """The staged copy of one piece of the last built step (int32; `u01` as raw bits)."""
+        o, n = self.layout[name]
+        return self._host.numpy()[o:o + n]
+
+    def resend(self, n_ints: int | None = None) -> None:
+        """Copies the staging buffer (or its first `n_ints` words) to the device again, after
+        the caller changed pieces of it in place.  The device addresses stay what they were."""
+        if self._copied is not None:
+            self._copied.synchronize()
+        n = self.total if n_ints is None else n_ints
+        self._dev[:n].copy_(self._host[:n], non_blocking=True)
+        self._copied.record()
+        self.last_h2d_bytes = n * 4

@@ -49,7 +49,7 @@ class GenerationResult:
 
 class Backend(Protocol):
     def start(self, prompts: list[list[int]], u01: list[float] | None,
-              histories: list[list[int]]) -> tuple[list[int], list[int]]:
+              histories: list[list[int]] | None) -> tuple[list[int], list[int]]:
         """Allocates a slot per prompt, runs all prompts in one step; returns (slots, first tokens)."""
 
     def decode(self, slots: list[int], tokens: list[int], u01: list[float] | None,
@@ -124,13 +124,15 @@ class GenerationLoop:
             if r.budget <= 0:
                 r.reason = "length"
         draw = not self.sampling.greedy
+        want_hist = self.sampling.has_penalties      # histories are only built for the penalties
         for group in plan_batches([len(r.prompt) for r in live], [r.budget for r in live],
                                   self.max_batch, self.token_budget, self.page):
             batch = [live[i] for i in group]
             stats.batches += 1
             t0 = self.clock()
             u = [r.rng.next() for r in batch] if draw else None
-            slots, toks = self.backend.start([r.prompt for r in batch], u, [r.history for r in batch])
+            slots, toks = self.backend.start([r.prompt for r in batch], u,
+                                             [r.history for r in batch] if want_hist else None)
             stats.prefill_ms += (self.clock() - t0) * 1e3
             stats.prefill_tokens += sum(len(r.prompt) for r in batch)
             for r, s in zip(batch, slots):
@@ -156,7 +158,7 @@ class GenerationLoop:
                     break
                 u = [r.rng.next() for r in active] if draw else None
                 toks = self.backend.decode([r.slot for r in active], [r.out[-1] for r in active], u,
-                                           [r.history for r in active])
+                                           [r.history for r in active] if want_hist else None)
                 stats.decode_steps += 1
                 stats.decode_tokens += len(active)
             stats.decode_ms += (self.clock() - t1) * 1e3
@@ -181,7 +183,8 @@ class EngineBackend:
         if n > self._out.numel():
             self._out = self._torch.empty(2 * n, dtype=self._torch.int32, device=self.engine.device)
             self._host = self._torch.empty(2 * n, dtype=self._torch.int32, pin_memory=True)
-        self.sampler.apply_penalties(logits, histories)
+        if histories is not None:
+            self.sampler.apply_penalties(logits, histories)
         self.sampler.sample(self._out, logits, batch.u01)
         self._host[:n].copy_(self._out[:n], non_blocking=True)
         self._torch.cuda.current_stream().synchronize()

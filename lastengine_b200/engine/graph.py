@@ -42,6 +42,8 @@ class DecodeGraph:
         self.out = torch.zeros(bucket, dtype=torch.int32, device=engine.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.batch = None
+        self.staged_slots: list[int] = []
+        self.cache_version = -1
         self.launches = 0
 
     def _run(self, batch) -> None:
@@ -68,6 +70,44 @@ class DecodeGraph:
             if not same:
                 self.graph = None      # the staging buffer moved: capture again
         self.batch = batch
+        self.staged_slots = list(slots)
+        return grow
+
+    def restage(self, slots: list[int], tokens: list[int], u01) -> dict[int, int] | None:
+        """The step after the one staged before, for the same sequences in the same order: only
+        the tokens, the positions (+1) and, where a sequence enters a new page, one entry of its
+        page table change.  Done in place in the staging buffer, then one copy.  Returns None
+        when the step is not of that kind (the caller stages it in full)."""
+        eng, bb = self.engine, self.builder
+        if self.batch is None or slots != self.staged_slots or eng.cache.state_version != self.cache_version:
+            return None
+        if any(g.spec.window > 0 for g in eng.cache.kv_groups):
+            return None      # windowed groups give pages back as they go: stage those steps in full
+        cache = eng.cache
+        n = len(slots)
+        page = cache.page_size
+        pos = bb.host_view("seq_pos0")
+        grow = {}
+        if bb._copied is not None:
+            bb._copied.synchronize()          # the last copy has read the buffer we are about to change
+        new_page = [i for i in range(n) if (int(pos[i]) + 1) % page == 0]
+        if new_page:
+            cache.reserve({slots[i]: 1 for i in new_page})
+            for gi, g in enumerate(cache.kv_groups):
+                tab = bb.host_view(f"table{gi}").reshape(self.bucket, -1)
+                for i in new_page:
+                    lst = g.seq_pages[slots[i]]
+                    if len(lst) > tab.shape[1]:
+                        return None
+                    tab[i, len(lst) - 1] = lst[-1]
+        bb.host_view("tokens")[:n] = tokens
+        pos[:n] += 1
+        bb.host_view("row_pos")[:n] += 1
+        if u01 is not None and "u01" in bb.layout:
+            bb.host_view("u01")[:n] = np.asarray(u01, dtype=np.float32).view(np.int32)
+        bb.resend(None if new_page else bb.head_total)
+        for s in slots:
+            grow[s] = 1
         return grow
 
     def launch(self) -> None:
@@ -116,9 +156,12 @@ class GraphBackend(EngineBackend):
         g = self.graphs.get(b)
         if g is None:
             g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width)
-        grow = g.stage(slots, tokens, u01)
+        grow = g.restage(slots, tokens, u01)
+        if grow is None:
+            grow = g.stage(slots, tokens, u01)
         g.launch()
         eng.cache.commit(grow)
+        g.cache_version = eng.cache.state_version
         n = len(slots)
         self._host[:n].copy_(g.out[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -277,7 +277,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
 
 # ----------------------------------------------------------------------------------------------
 STORE, ACCUMULATE, SWIGLU = 0, 1, 2
-SMALL_M = 64  # rows up to which the weight-streaming kernel is used
+SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcgen05 tiles
 
 
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,

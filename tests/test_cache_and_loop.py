@@ -153,8 +153,9 @@ class Scripted:
         return t
 
     def decode(self, slots, tokens, u01, histories):
-        for s, t, h in zip(slots, tokens, histories):
-            assert t == self.script[self.owner[s]][self.count[s] - 1] and h[-1] == t
+        for i, (s, t) in enumerate(zip(slots, tokens)):
+            assert t == self.script[self.owner[s]][self.count[s] - 1]
+            assert histories is None or histories[i][-1] == t
         self.log.append(("decode", list(slots), u01))
         return [self._next(s) for s in slots]
 
@@ -196,6 +197,17 @@ def test_loop_context_budget_and_sampling_streams():
     assert u == [XorShift64(11, stream=0).next()]
     with pytest.raises(ValueError, match="empty prompt"):
         loop.run([[]])
+
+
+def test_loop_builds_histories_only_for_penalties():
+    be = Scripted({0: [1, 2, 3]})
+    GenerationLoop(be, SamplingParams(temperature=0.0), max_new_tokens=3).run([[0, 5]])
+    be2 = Scripted({0: [1, 2, 3]})
+    seen = []
+    orig = be2.decode
+    be2.decode = lambda slots, tokens, u01, histories: (seen.append(histories), orig(slots, tokens, u01, histories))[1]
+    GenerationLoop(be2, SamplingParams(temperature=0.0, repeat_penalty=1.2), max_new_tokens=3).run([[0, 5]])
+    assert seen and seen[0] == [[0, 5, 1]]
 
 
 def test_plan_batches_respects_cache_room():

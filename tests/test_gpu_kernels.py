@@ -393,7 +393,8 @@ def test_penalties():
 
 # ---- the tcgen05 matrix product ------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (128, 256, 128), (65, 48, 72), (200, 100, 200), (300, 520, 136),
-                                    (2048, 2048, 2048), (513, 6144, 2048), (1000, 2048, 5632)])
+                                    (2048, 2048, 2048), (513, 6144, 2048), (1000, 2048, 5632),
+                                    (17, 2048, 256), (64, 352, 128), (100, 6144, 64), (33, 11264, 192)])
 def test_linear_tc(M, N, K_):
     """Tensor-memory accumulation against float64, at tile-aligned sizes and at sizes where rows,
     columns and k all run past the last tile; store, add-to-residual, and both result types."""
@@ -413,7 +414,7 @@ def test_linear_tc(M, N, K_):
     assert err(base, b0.cpu().double() + want) < 2e-5
 
 
-@pytest.mark.parametrize("M,F,D", [(128, 64, 64), (70, 16, 40), (300, 160, 96), (2048, 5632, 2048)])
+@pytest.mark.parametrize("M,F,D", [(128, 64, 64), (70, 16, 40), (300, 160, 96), (2048, 5632, 2048), (40, 5632, 128), (64, 1024, 64)])
 def test_linear_tc_swiglu_epilogue(M, F, D):
     from lastengine_b200.parts.ffn import fuse_gate_up
     x = gen(M, D, seed=103, dtype=torch.bfloat16)
