@@ -441,3 +441,25 @@ def test_linear_tc_strided_operand_and_small_kernel_agree():
                                   torch.cuda.current_stream().cuda_stream)
     assert err(a, x.double().cpu() @ w.double().cpu().T) < 2e-5
     assert err(a, b) < 2e-6
+
+
+def test_shortconv_kernels_against_the_references_own():
+    """The engine's convolution kernels (rows + state, and the one-launch decode form) on the inputs
+    of tests/golden/shortconv_golden.npz, which holds what the reference's kernels gave."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "shortconv_golden.npz"))
+    for case in range(3):
+        bcx, w = torch.from_numpy(g[f"bcx{case}"]), torch.from_numpy(g[f"w{case}"])
+        T, n, lc = bcx.shape[0], w.shape[0], w.shape[1]
+        for mode in ("chunk", "steps"):
+            state = torch.zeros(3, n, lc - 1, device=DEV)
+            state[2] = torch.from_numpy(g[f"state_in{case}"]).to(DEV)
+            y = torch.empty(T, n, device=DEV)
+            bb = builder()
+            if mode == "chunk":
+                K().shortconv(y, bcx.to(DEV), w.to(DEV), None, state, bb.build([2], [[0] * T], [0], [], {}), lc)
+            else:
+                for t in range(T):
+                    K().shortconv(y[t:t + 1], bcx[t:t + 1].to(DEV), w.to(DEV), None, state, bb.build([2], [[0]], [t], [], {}), lc)
+            assert err(y, torch.from_numpy(g[f"y{case}"])) < 1e-6, (case, mode)
+            assert err(state[2], torch.from_numpy(g[f"state_out{case}"])) < 1e-6, (case, mode)

@@ -122,3 +122,25 @@ def test_sampler_by_hand():
     assert [P.sample(lg, 1.0, 2, 1.0, 0.0, u) for u in (0.1, 0.7)] == [0, 1]            # top-2: 0.625 / 0.375
     assert P.sample(lg, 1.0, 40, 0.7, 0.0, 0.99) == 1                                   # top-p keeps {0,1}
     assert P.sample(lg, 1.0, 40, 1.0, 0.4, 0.99) == 1                                   # min-p 0.4*0.5 cuts 0.15
+
+
+def test_short_conv_against_the_references_own_kernels():
+    """tests/golden/shortconv_golden.npz holds inputs and outputs of the reference's two
+    short-convolution kernels (made by tests/golden/make_shortconv_golden.py from the reference
+    checkout).  With identity projections the plain convolution must reproduce them: the B/C/x
+    split order, the tap order, and the state layout (oldest value first)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "shortconv_golden.npz"))
+    for case in range(3):
+        bcx, w = torch.from_numpy(g[f"bcx{case}"]).double(), torch.from_numpy(g[f"w{case}"]).double()
+        T, n = bcx.shape[0], w.shape[0]
+        lc = w.shape[1]
+        # in_proj: the plain function computes bcx = h @ in_proj^T; feed bcx itself through a selector
+        p = {"in_proj.weight": torch.eye(3 * n, dtype=torch.float64), "conv.weight": w.reshape(n, 1, lc),
+             "out_proj.weight": torch.eye(n, dtype=torch.float64)}
+        # the reference's state is [channel][oldest..newest]; the plain function carries rows of time
+        st_in = torch.from_numpy(g[f"state_in{case}"]).double().T.contiguous()
+        # identity projections: the 3n-wide input rows are (B, C, x) themselves
+        out, st = P.short_conv(bcx, p, T, D=n, Lc=lc, state=st_in)
+        assert torch.allclose(out, torch.from_numpy(g[f"y{case}"]).double(), atol=1e-5)
+        assert torch.allclose(st.T, torch.from_numpy(g[f"state_out{case}"]).double(), atol=1e-6)
