@@ -119,26 +119,42 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     for (int e = 0; e < 4; e++) acc[n][e] = 0.f;
 
   const int* table = block_table + (size_t)b * bt_width;
-  for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS) {
+  uint4 kf[4][KB], vf[NT];      // the block being multiplied
+  uint4 kn[4][KB], vn[NT];      // this warp's next block, in flight meanwhile (small heads only)
+  constexpr bool PREFETCH = HD <= 64;
+  auto load_block = [&](int blk, uint4 (&kd)[4][KB], uint4 (&vd)[NT]) {
     const int key0 = blk * 32;
     const int page = table[key0 / page_size];
     const int off = key0 % page_size;
     const bf16* kbase = k_pool + (((size_t)page * nkv + kvh) * page_size + off) * HD;
     const bf16* vbase = v_pool + ((size_t)page * nkv + kvh) * HD * page_size + off;
     // keys: tile t, column n = r -> position 8*(r/2) + 2t + (r%2)
-    uint4 kf[4][KB];
 #pragma unroll
     for (int t = 0; t < 4; t++) {
       const int kp = 8 * (r >> 1) + 2 * t + (r & 1);
 #pragma unroll
       for (int j = 0; j < KB; j++)
-        kf[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
+        kd[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
     }
     // values: output tile n, dimension 8n + r, positions 8c..8c+7 of the block
-    uint4 vf[NT];
 #pragma unroll
     for (int n = 0; n < NT; n++)
-      vf[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+      vd[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+  };
+  if (PREFETCH && blk_lo + warp < blk_hi) load_block(blk_lo + warp, kn, vn);
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS) {
+    const int key0 = blk * 32;
+    if (PREFETCH) {
+#pragma unroll
+      for (int t = 0; t < 4; t++)
+#pragma unroll
+        for (int j = 0; j < KB; j++) kf[t][j] = kn[t][j];
+#pragma unroll
+      for (int n = 0; n < NT; n++) vf[n] = vn[n];
+      if (blk + ATD_WARPS < blk_hi) load_block(blk + ATD_WARPS, kn, vn);
+    } else {
+      load_block(blk, kf, vf);
+    }
     const bool partial = key0 < key_lo || key0 + 32 > kv_len;
     if (partial) {
 #pragma unroll

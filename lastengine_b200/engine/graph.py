@@ -69,6 +69,8 @@ class DecodeGraph:
                     and all(batch.tables[k].data_ptr() == self.batch.tables[k].data_ptr() for k in batch.tables))
             if not same:
                 self.graph = None      # the staging buffer moved: capture again
+        # what is baked into the graph must not depend on how long the sequences are today
+        batch.max_kvlen = self.width * eng.cache.page_size
         self.batch = batch
         self.staged_slots = list(slots)
         return grow

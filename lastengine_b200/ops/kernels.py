@@ -40,6 +40,7 @@ def _declare(L) -> None:
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
+        "leb_gemm_bf16_small_norm": [P, I, P, I, P, F, P, I, I, I, I, I, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
         "leb_moe_align": [P, P, P, P, I, I, P],
         "leb_moe_combine": [P, P, P, P, I, I, I, I, P],
@@ -216,11 +217,17 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
 
 
 def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
-    """How many blocks share one sequence's key range in a decode step (1 for prompts)."""
+    """How many blocks share one sequence's key range in a decode step (1 for prompts).
+
+    Measured on B200 (head size 64, 8 kv heads): about 1024 positions per block is best at any
+    batch size, and with few sequences more splits are worth it until some 128 blocks run.
+    """
     if batch.max_qlen != 1:
         return 1
+    kv = max(int(batch.max_kvlen), 1)
     per = batch.n_seqs * nkv * ((G + 15) // 16)
-    return max(1, min(32, (4 * sm_count) // max(per, 1)))
+    want = max(-(-kv // 1024), -(-128 // max(per, 1)))
+    return max(1, min(32, want, -(-kv // 128)))
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -280,7 +287,35 @@ STORE, ACCUMULATE, SWIGLU = 0, 1, 2
 SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcgen05 tiles
 
 
-def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
+# Forming the norm inside the product saves a launch per product but puts the sum of squares in
+# front of every block's weight stream; measured on B200 (hidden 2048, batch 1 and 8) a decode
+# step got 10% slower, so it is off.  The path stays tested.
+FUSE_NORM = False
+
+
+class NormedInput:
+    """RMSNorm(x) that has not been computed yet: the float residual rows `x`, the norm's weight
+    and eps.  `linear` forms it inside the matrix product when it can (bfloat16, few rows);
+    `materialize` runs the norm kernel into `buf` for everything else."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, buf: torch.Tensor):
+        self.x, self.weight, self.eps, self.buf = x, weight, eps, buf
+        self._done = False
+        self.shape, self.dtype, self.device = buf.shape, buf.dtype, buf.device
+
+    def materialize(self) -> torch.Tensor:
+        if not self._done:
+            rmsnorm(self.buf, self.x, self.weight, self.eps)
+            self._done = True
+        return self.buf
+
+
+def as_tensor(h) -> torch.Tensor:
+    """The activation tensor of `h`, computing a pending norm if there is one."""
+    return h.materialize() if isinstance(h, NormedInput) else h
+
+
+def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
            group_offsets: torch.Tensor | None = None, rows_hint: int = 0, streaming: bool = False) -> None:
     """out (+)= x . w^T  with w [N, K] (or [E, N, K] with group_offsets [E+1] over the rows).
 
@@ -290,6 +325,20 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
     With more than SMALL_M rows bfloat16 products go to the tcgen05 kernel, unless `streaming`
     asks for the weight-streaming kernel whatever the row count.
     """
+    if isinstance(x, NormedInput):
+        nx = x
+        M, K = nx.shape
+        if (not nx._done and nx.dtype == torch.bfloat16 and M <= SMALL_M and group_offsets is None
+                and epilogue in (STORE, SWIGLU) and K % 8 == 0 and nx.x.stride(0) % 4 == 0):
+            _cuda(w, "linear.w", torch.bfloat16)
+            _cuda(out, "linear.out", contiguous=False)
+            N = w.shape[0]
+            assert w.shape[1] == K and out.shape == (M, N // 2 if epilogue == SWIGLU else N)
+            _check(lib().leb_gemm_bf16_small_norm(_ptr(out), _dt(out, "linear.out"), _ptr(nx.x), nx.x.stride(0),
+                                                  _ptr(nx.weight), float(nx.eps), _ptr(w), M, N, K, out.stride(0),
+                                                  epilogue, _stream()))
+            return
+        x = nx.materialize()
     _cuda(x, "linear.x", contiguous=False)
     _cuda(w, "linear.w", x.dtype)
     _cuda(out, "linear.out", contiguous=False)
