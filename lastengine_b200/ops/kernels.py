@@ -53,6 +53,9 @@ def _declare(L) -> None:
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
         "leb_attention_prefill_supported": [I, I, I, I],
         "leb_attention_prefill": [P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+        "leb_gemm_bf16_skinny_slices": [I, I],
+        "leb_gemm_bf16_skinny_supported": [P, P, I, I, I],
+        "leb_gemm_bf16_skinny": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gemm_bf16_tc_supported": [P, P, I, I],
         "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
     }
@@ -371,6 +374,11 @@ def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
         raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
     hint = rows_hint if rows_hint > 0 else M
     tc = _OPTIONAL_TC[0]
+    # few dozen rows: W as the wide operand with K sliced over blocks, unless N alone already gives
+    # every SM several tiles (the output head), where the persistent kernel streams W better
+    if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296
+            and linear_skinny(out, x, w, epilogue)):
+        return
     if tc is not None and not streaming and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
         return
     _check(L.leb_gemm_bf16_small(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
@@ -495,6 +503,36 @@ def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int
         return False
     _check(L.leb_gemm_bf16_tc(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                               out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
+    return True
+
+
+SKINNY_M = 128   # rows up to which W is the wide tcgen05 operand and K is sliced over blocks
+_skinny_ws: dict[int, list[torch.Tensor]] = {}
+
+
+def _skinny_workspace(device: torch.device, n_floats: int) -> torch.Tensor:
+    """Float scratch for the K slices.  Grows by adding buffers and never frees one, so that a
+    captured graph that points at an older buffer stays valid."""
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    bufs = _skinny_ws.setdefault(i, [])
+    if not bufs or bufs[-1].numel() < n_floats:
+        bufs.append(torch.empty(max(n_floats, 1 << 22), dtype=torch.float32, device=device))
+    return bufs[-1]
+
+
+def linear_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE) -> bool:
+    """out (+)= x . w^T for 1..128 rows with W as the wide tcgen05 operand and K sliced over blocks."""
+    L = lib()
+    M, K = x.shape
+    N = w.shape[0]
+    if not L.leb_gemm_bf16_skinny_supported(_ptr(x), _ptr(w), M, K, x.stride(0)):
+        return False
+    slices = L.leb_gemm_bf16_skinny_slices(N, K)
+    if epilogue == SWIGLU:
+        slices = max(slices, 2)
+    part = _skinny_workspace(x.device, slices * M * N) if slices > 1 else None
+    _check(L.leb_gemm_bf16_skinny(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
+                                  out.stride(0), epilogue, _ptr(part), slices, _ptr(_status_word(x.device)), _stream()))
     return True
 
 

@@ -485,3 +485,36 @@ def test_linear_with_pending_norm(M, N, K_, ep):
     if ep == 2:
         ref = P.silu(ref[:, 0::1].reshape(M, N // 32, 2, 16)[:, :, 0].reshape(M, -1)) * ref.reshape(M, N // 32, 2, 16)[:, :, 1].reshape(M, -1)
     assert err(got, ref) < 4e-3
+
+
+@pytest.mark.parametrize("M,N,K_", [(17, 2048, 2048), (64, 352, 128), (100, 6144, 64), (33, 11264, 192), (128, 100, 200),
+                                    (1, 128, 64), (16, 48, 72), (48, 2048, 5632), (64, 65536, 256)])
+def test_linear_skinny(M, N, K_):
+    """The swapped-operand tcgen05 product with K sliced over blocks: store, add to residual, both
+    result types, sizes that leave partial tiles and slices."""
+    x, w = gen(M, K_, seed=120, dtype=torch.bfloat16), gen(N, K_, seed=121, scale=0.05, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    assert K().linear_skinny(out, x.to(DEV), w.to(DEV))
+    K().check_device_status()
+    assert err(out, want) < 2e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear_skinny(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=122).to(DEV)
+    b0 = base.clone()
+    K().linear_skinny(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    K().check_device_status()
+    assert err(base, b0.cpu().double() + want) < 2e-5
+
+
+@pytest.mark.parametrize("M,F,D", [(64, 5632, 2048), (20, 16, 40), (100, 160, 96)])
+def test_linear_skinny_swiglu(M, F, D):
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    x = gen(M, D, seed=123, dtype=torch.bfloat16)
+    w1, w3 = gen(F, D, seed=124, scale=0.05, dtype=torch.bfloat16), gen(F, D, seed=125, scale=0.05, dtype=torch.bfloat16)
+    want = P.silu(x.double() @ w1.double().T) * (x.double() @ w3.double().T)
+    out = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    assert K().linear_skinny(out, x.to(DEV), fuse_gate_up(w1, w3, True).to(DEV), K().SWIGLU)
+    K().check_device_status()
+    assert err(out, want) < 6e-3
