@@ -162,20 +162,9 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
       vd[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
   };
   constexpr bool PREFETCH = HD <= 64;   // larger heads have no registers to spare for a second block
-  if (PREFETCH) load_block(blk_first, kn, vn);
-  for (int blk = blk_first; blk <= blk_last; blk++) {
+  // one block of 32 positions against this warp's rows
+  auto compute = [&](uint4 (&kf)[4][KB], uint4 (&vf)[NT], int blk) {
     const int key0 = blk * 32;
-    if (PREFETCH) {
-#pragma unroll
-      for (int t = 0; t < 4; t++)
-#pragma unroll
-        for (int j = 0; j < KB; j++) kf[t][j] = kn[t][j];
-#pragma unroll
-      for (int n = 0; n < NT; n++) vf[n] = vn[n];
-      if (blk < blk_last) load_block(blk + 1, kn, vn);
-    } else {
-      load_block(blk, kf, vf);
-    }
     if (key0 + 32 > kv_len) {
 #pragma unroll
       for (int n = 0; n < NT; n++) vf[n] = mask_tail(vf[n], key0 + 8 * c, kv_len);
@@ -246,15 +235,36 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
         psum[hh] += __shfl_xor_sync(0xffffffffu, psum[hh], 2);
         l[mt][hh] = l[mt][hh] * corr[hh] + psum[hh];
       }
+      // after the first blocks a row's maximum seldom moves: skip the rescaling then
+      const bool moved = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
 #pragma unroll
       for (int n = 0; n < NT; n++) {
-        acc[mt][n][0] *= corr[0];
-        acc[mt][n][1] *= corr[0];
-        acc[mt][n][2] *= corr[1];
-        acc[mt][n][3] *= corr[1];
+        if (moved) {
+          acc[mt][n][0] *= corr[0];
+          acc[mt][n][1] *= corr[0];
+          acc[mt][n][2] *= corr[1];
+          acc[mt][n][3] *= corr[1];
+        }
         mma16816p(acc[mt][n], pa[0][0], pa[0][1], pa[1][0], pa[1][1], vf[n].x, vf[n].y);
         mma16816p(acc[mt][n], pa[2][0], pa[2][1], pa[3][0], pa[3][1], vf[n].z, vf[n].w);
       }
+    }
+  };
+  if (PREFETCH) {
+    // two sets of fragments take turns: one is multiplied while the other is in flight
+    load_block(blk_first, kf, vf);
+    for (int blk = blk_first; blk <= blk_last; blk += 2) {
+      if (blk + 1 <= blk_last) load_block(blk + 1, kn, vn);
+      compute(kf, vf, blk);
+      if (blk + 1 <= blk_last) {
+        if (blk + 2 <= blk_last) load_block(blk + 2, kf, vf);
+        compute(kn, vn, blk + 1);
+      }
+    }
+  } else {
+    for (int blk = blk_first; blk <= blk_last; blk++) {
+      load_block(blk, kf, vf);
+      compute(kf, vf, blk);
     }
   }
 
