@@ -16,51 +16,97 @@
 // time).  The page of position p of sequence b is block_table[b][p / page_size].
 #include "common.cuh"
 
+constexpr int ROPE_WARPS = 8;   // warps of a block; each takes every 8th head of its row
+constexpr int VT_ROWS = 32;     // rows of a value tile
+constexpr int VT_DIMS = 64;     // dimensions of a value tile
+
+// Blocks [0, M): one row each; its warps norm and rotate the q and k heads (sine and cosine of
+// the row's position are computed once per block, not per head) and write q and the cached k.
+// Blocks [M, M + tiles * nkv): a tile of VT_ROWS rows of one kv head's values, turned through
+// shared memory so that a warp writes 32 consecutive positions of one dimension (64 bytes in
+// bfloat16) instead of 32 scattered elements.  Every row's page and offset is looked up on its
+// own, so rows of different sequences or pages in one tile are fine.
 template <typename T, typename CT>
-__global__ void qk_rope_store_kernel(
+__global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     T* __restrict__ q_out, const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in,
     const T* __restrict__ v_in, int kv_stride, CT* __restrict__ k_pool, CT* __restrict__ v_pool,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ row_seq,
     const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
-    const float* __restrict__ inv_freq, int rope_dim, int neox, int nh, int nkv, int hd,
+    const float* __restrict__ inv_freq, int rope_dim, int neox, int M, int nh, int nkv, int hd,
     int page_size) {
-  extern __shared__ float sm[];  // one head vector per warp
+  extern __shared__ float sm[];
   pdl_wait();
-  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if ((int)blockIdx.x >= M) {
+    // ---- value tile ----
+    CT* tile = reinterpret_cast<CT*>(sm);                       // [VT_ROWS][VT_DIMS + pad]
+    constexpr int LD = VT_DIMS + (sizeof(CT) == 2 ? 2 : 1);     // odd number of 32-bit words
+    __shared__ long long dst[VT_ROWS];                          // element offset of (row, dim 0), or -1
+    int t = blockIdx.x - M;
+    int kvh = t % nkv, m0 = (t / nkv) * VT_ROWS;
+    if (threadIdx.x < VT_ROWS) {
+      int m = m0 + threadIdx.x;
+      long long off = -1;
+      if (m < M) {
+        int b = row_seq[m], pos = row_pos[m];
+        if (seq_slot[b] >= 0) {
+          int page = block_table[(size_t)b * bt_width + pos / page_size];
+          if (page >= 0) off = ((long long)page * nkv + kvh) * hd * page_size + pos % page_size;
+        }
+      }
+      dst[threadIdx.x] = off;
+    }
+    for (int d0 = 0; d0 < hd; d0 += VT_DIMS) {
+      int nd = min(VT_DIMS, hd - d0);
+      __syncthreads();
+      for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
+        int r = i / VT_DIMS, d = i % VT_DIMS;
+        if (d < nd && m0 + r < M)
+          tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]));
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
+        int d = i / VT_ROWS, r = i % VT_ROWS;
+        if (d < nd && dst[r] >= 0) v_pool[dst[r] + (size_t)(d0 + d) * page_size] = tile[r * LD + d];
+      }
+    }
+    return;
+  }
+  // ---- one row: q and k heads ----
   int m = blockIdx.x;
-  int head = blockIdx.y * nwarps + warp;  // [0,nh): q; [nh,nh+nkv): k; [nh+nkv, nh+2nkv): v
-  int total = nh + (k_in ? 2 * nkv : 0);
-  if (head >= total) return;
   int b = row_seq[m];
   int slot = seq_slot[b];
   int pos = row_pos[m];
-  float* v = sm + warp * hd;
-
-  const T* src;
-  const float* nw = nullptr;
-  int kind;  // 0 q, 1 k, 2 v
-  if (head < nh) {
-    kind = 0;
-    src = q_in + (size_t)m * q_stride + (size_t)head * hd;
-    nw = q_norm_w;
-  } else if (head < nh + nkv) {
-    kind = 1;
-    src = k_in + (size_t)m * kv_stride + (size_t)(head - nh) * hd;
-    nw = k_norm_w;
-  } else {
-    kind = 2;
-    src = v_in + (size_t)m * kv_stride + (size_t)(head - nh - nkv) * hd;
+  int half = rope_dim / 2;
+  float* cs = sm;                                   // [half] cosine, [half] sine
+  float* v = sm + 2 * half + warp * hd;             // one head vector per warp
+  if (inv_freq) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float th = (float)pos * inv_freq[i];
+      cs[i] = cosf(th);
+      cs[half + i] = sinf(th);
+    }
   }
-  if (kind != 0 && slot < 0) return;  // padding rows own no cache
-
-  float ss = 0.f;
-  for (int i = lane; i < hd; i += 32) {
-    float x = to_f32(src[i]);
-    v[i] = x;
-    ss += x * x;
+  __syncthreads();
+  int total = nh + (k_in ? nkv : 0);
+  long long kdst = -1;
+  if (k_in && slot >= 0) {
+    int page = block_table[(size_t)b * bt_width + pos / page_size];
+    if (page >= 0) kdst = ((long long)page * nkv * page_size + pos % page_size) * hd;
   }
-  if (kind != 2) {
+  for (int head = warp; head < total; head += ROPE_WARPS) {
+    bool is_q = head < nh;
+    if (!is_q && kdst < 0) continue;  // padding rows and positions outside a window own no cache
+    const T* src = is_q ? q_in + (size_t)m * q_stride + (size_t)head * hd
+                        : k_in + (size_t)m * kv_stride + (size_t)(head - nh) * hd;
+    const float* nw = is_q ? q_norm_w : k_norm_w;
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+      float x = to_f32(src[i]);
+      v[i] = x;
+      ss += x * x;
+    }
     if (nw) {
       ss = warp_sum(ss);
       float r = 1.0f / sqrtf(ss / (float)hd + eps);
@@ -69,32 +115,23 @@ __global__ void qk_rope_store_kernel(
     }
     __syncwarp();
     if (inv_freq) {
-      int half = rope_dim / 2;
       for (int i = lane; i < half; i += 32) {
-        float th = (float)pos * inv_freq[i];
-        float s = sinf(th), c = cosf(th);
+        float c = cs[i], s = cs[half + i];
         int ia = neox ? i : 2 * i, ib = neox ? i + half : 2 * i + 1;
         float a = v[ia], bb = v[ib];
         v[ia] = a * c - bb * s;
         v[ib] = a * s + bb * c;
       }
     }
-  }
-  __syncwarp();
-  if (kind == 0) {
-    T* o = q_out + ((size_t)m * nh + head) * hd;
-    for (int i = lane; i < hd; i += 32) o[i] = from_f32<T>(v[i]);
-  } else {
-    int kvh = kind == 1 ? head - nh : head - nh - nkv;
-    int page = block_table[(size_t)b * bt_width + pos / page_size];
-    if (page < 0) return;  // a position the cache no longer holds (outside a window)
-    if (kind == 1) {
-      CT* o = k_pool + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * hd;
-      for (int i = lane; i < hd; i += 32) o[i] = from_f32<CT>(v[i]);
+    __syncwarp();
+    if (is_q) {
+      T* o = q_out + ((size_t)m * nh + head) * hd;
+      for (int i = lane; i < hd; i += 32) o[i] = from_f32<T>(v[i]);
     } else {
-      CT* o = v_pool + ((size_t)page * nkv + kvh) * hd * page_size + pos % page_size;
-      for (int i = lane; i < hd; i += 32) o[(size_t)i * page_size] = from_f32<CT>(v[i]);
+      CT* o = k_pool + kdst + (size_t)(head - nh) * page_size * hd;
+      for (int i = lane; i < hd; i += 32) o[i] = from_f32<CT>(v[i]);
     }
+    __syncwarp();
   }
 }
 
@@ -108,20 +145,20 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
   if (M <= 0) return 0;
   LEB_REQUIRE(hd >= 2 && hd <= 512, "leb_qk_rope_store: head_dim %d outside 2..512", hd);
   LEB_REQUIRE(rope_dim <= hd && rope_dim % 2 == 0, "leb_qk_rope_store: rope_dim %d does not fit head_dim %d", rope_dim, hd);
-  const int nwarps = 4;
-  int total = nh + (k_in ? 2 * nkv : 0);
-  dim3 grid(M, ceil_div(total, nwarps)), block(32 * nwarps);
-  size_t smem = (size_t)nwarps * hd * sizeof(float);
+  int tiles = k_in ? ceil_div(M, VT_ROWS) * nkv : 0;
+  dim3 grid(M + tiles), block(32 * ROPE_WARPS);
+  size_t smem = max((size_t)(rope_dim + ROPE_WARPS * hd) * sizeof(float),
+                    (size_t)VT_ROWS * (VT_DIMS + 2) * sizeof(float));
   if (dtype == LEB_F32)
     leb_launch(qk_rope_store_kernel<float, float>, grid, block, smem, st,
         (float*)q_out, (const float*)q_in, q_stride, (const float*)k_in, (const float*)v_in,
         kv_stride, (float*)k_pool, (float*)v_pool, block_table, bt_width, row_seq, row_pos,
-        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, nh, nkv, hd, page_size);
+        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size);
   else if (dtype == LEB_BF16)
     leb_launch(qk_rope_store_kernel<bf16, bf16>, grid, block, smem, st,
         (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
         (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-        k_norm_w, eps, inv_freq, rope_dim, neox, nh, nkv, hd, page_size);
+        k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size);
   else
     return leb_fail("leb_qk_rope_store: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_qk_rope_store");

@@ -106,6 +106,97 @@ __global__ void shortconv_rows_bf16x8_kernel(bf16* __restrict__ y, const bf16* _
   *yo = o;
 }
 
+// The same again for the usual short lengths: a thread owns 8 channels over CONV_CHUNK consecutive
+// rows and keeps the last LC-1 products B*x in registers, so each row's B, C and x are loaded
+// once instead of LC times.  Taps, bias and order of the sum are those of the kernels above, so
+// the results are the same bit for bit.
+constexpr int CONV_CHUNK = 8;
+
+__device__ __forceinline__ void conv_mul8(float* o, const uint4& a, const uint4& b) {
+  const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const float2 af = __bfloat1622float2(ap[e]), bf = __bfloat1622float2(bp[e]);
+    o[2 * e] = af.x * bf.x;
+    o[2 * e + 1] = af.y * bf.y;
+  }
+}
+
+template <int LC>
+__global__ void __launch_bounds__(128) shortconv_rows_bf16x8_chunk_kernel(
+    bf16* __restrict__ y, const bf16* __restrict__ bcx, const float* __restrict__ w,
+    const float* __restrict__ bias, const float* __restrict__ state, const int* __restrict__ row_seq,
+    const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart, int M, int D) {
+  const int m0 = blockIdx.x * CONV_CHUNK;
+  const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (ch0 >= D) return;
+  float wt[LC][8], bs[8], hist[LC - 1][8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) {
+    bs[e] = bias ? bias[ch0 + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < LC; j++) wt[j][e] = w[(size_t)(ch0 + e) * LC + j];
+  }
+#pragma unroll
+  for (int k = 0; k < LC - 1; k++) {  // products of the rows just before the chunk
+    const int row = m0 - (LC - 1) + k;
+    if (row >= 0) {
+      const bf16* r = bcx + (size_t)row * 3 * D;
+      conv_mul8(hist[k], *reinterpret_cast<const uint4*>(r + ch0), *reinterpret_cast<const uint4*>(r + 2 * D + ch0));
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) hist[k][e] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < CONV_CHUNK; rr++) {
+    const int m = m0 + rr;
+    if (m >= M) break;
+    const bf16* r = bcx + (size_t)m * 3 * D;
+    const uint4 Bv = *reinterpret_cast<const uint4*>(r + ch0);
+    const uint4 Cv = *reinterpret_cast<const uint4*>(r + D + ch0);
+    const uint4 Xv = *reinterpret_cast<const uint4*>(r + 2 * D + ch0);
+    const int b = row_seq[m];
+    const int slot = seq_slot[b];
+    const int i = m - seq_qstart[b];
+    float cur[8], acc[8];
+    conv_mul8(cur, Bv, Xv);
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[e] = bs[e];
+#pragma unroll
+    for (int j = 0; j < LC - 1; j++) {
+      const int src = i - (LC - 1) + j;  // row of this sequence in this step; negative: before it
+      if (src >= 0) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += wt[j][e] * hist[j][e];
+      } else if (slot >= 0) {
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+          acc[e] += wt[j][e] * state[((size_t)slot * D + ch0 + e) * (LC - 1) + (LC - 1) + src];
+      }
+    }
+    const __nv_bfloat162* Cp = reinterpret_cast<const __nv_bfloat162*>(&Cv);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float2 cf = __bfloat1622float2(Cp[e]);
+      __nv_bfloat162 v = __floats2bfloat162_rn(cf.x * (acc[2 * e] + wt[LC - 1][2 * e] * cur[2 * e]),
+                                               cf.y * (acc[2 * e + 1] + wt[LC - 1][2 * e + 1] * cur[2 * e + 1]));
+      op[e] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    if (slot < 0) o = make_uint4(0, 0, 0, 0);  // padding row
+    *reinterpret_cast<uint4*>(y + (size_t)m * D + ch0) = o;
+#pragma unroll
+    for (int k = 0; k + 1 < LC - 1; k++)
+#pragma unroll
+      for (int e = 0; e < 8; e++) hist[k][e] = hist[k + 1][e];
+#pragma unroll
+    for (int e = 0; e < 8; e++) hist[LC - 2][e] = cur[e];
+  }
+}
+
 // New state of each sequence: the last Lc-1 values of (old state ++ bx of this step's rows).
 template <typename T>
 __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
@@ -193,7 +284,15 @@ LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, c
     shortconv_state_kernel<float><<<g2, block, 0, st>>>((const float*)bcx, state, seq_slot,
                                                         seq_qstart, seq_qlen, D, Lc);
   } else if (dtype == LEB_BF16) {
-    if (D % 8 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)bcx % 16) == 0)
+    const bool vec = D % 8 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)bcx % 16) == 0;
+    const dim3 gc(ceil_div(M, CONV_CHUNK), ceil_div(D / 8, 128));
+    if (vec && Lc == 3 && M >= 256)
+      shortconv_rows_bf16x8_chunk_kernel<3><<<gc, block, 0, st>>>(
+          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, M, D);
+    else if (vec && Lc == 4 && M >= 256)
+      shortconv_rows_bf16x8_chunk_kernel<4><<<gc, block, 0, st>>>(
+          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, M, D);
+    else if (vec)
       shortconv_rows_bf16x8_kernel<<<dim3(M, ceil_div(D / 8, 128)), block, 0, st>>>(
           (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, D, Lc);
     else

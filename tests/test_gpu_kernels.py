@@ -177,6 +177,37 @@ def test_shortconv_with_state(dtype, Lc, D):
     assert float(state[1].min()) == 7.0 and float(state[5].max()) == 7.0     # other slots untouched
 
 
+@pytest.mark.parametrize("Lc,D", [(3, 136), (4, 72), (3, 2048)])
+def test_shortconv_many_rows(Lc, D):
+    """Prompts long enough for the kernel that walks several rows per thread: sequences start in
+    the middle of a thread's rows, one is shorter than the filter, one slot is padding, and one
+    starts from a state that is not zero."""
+    lens = [1, 301, 2, 130, 77]
+    slots = [3, 1, -1, 0, 2]
+    w = gen(D, Lc, seed=18)
+    bcx = [gen(n, 3 * D, seed=40 + i, dtype=torch.bfloat16) for i, n in enumerate(lens)]
+    state = torch.zeros(4, D, Lc - 1, device=DEV)
+    old = gen(D, Lc - 1, seed=19)
+    state[2] = old.to(DEV)
+    batch = builder().build(slots, [[0] * n for n in lens], [0, 0, 0, 0, 5], [], {})
+    y = torch.full((sum(lens), D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K().shortconv(y, torch.cat(bcx).to(DEV), w.to(DEV), None, state, batch, Lc)
+    r0 = 0
+    for i, n in enumerate(lens):
+        got = y[r0:r0 + n].float().cpu()
+        r0 += n
+        if slots[i] < 0:
+            assert float(got.abs().max()) == 0.0
+            continue
+        x = bcx[i].double()
+        bx = x[:, :D] * x[:, 2 * D:]
+        before = old.double().T if slots[i] == 2 else torch.zeros(Lc - 1, D, dtype=torch.float64)
+        padded = torch.cat([before, bx])
+        acc = sum(padded[j:j + n] * w.double()[:, j][None] for j in range(Lc))
+        assert err(got, x[:, D:2 * D] * acc) < 5e-3, i
+        assert err(state[slots[i]].cpu().T, padded[-(Lc - 1):]) < 1e-6, i
+
+
 # ---- rotation and cache write ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rope_dim", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80)])
