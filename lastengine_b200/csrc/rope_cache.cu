@@ -16,16 +16,55 @@
 // time).  The page of position p of sequence b is block_table[b][p / page_size].
 #include "common.cuh"
 
-constexpr int ROPE_WARPS = 8;   // warps of a block; each takes every 8th head of its row
+constexpr int ROPE_WARPS = 8;   // warps of a block; each takes one head of the block's row
 constexpr int VT_ROWS = 32;     // rows of a value tile
 constexpr int VT_DIMS = 64;     // dimensions of a value tile
 
-// Blocks [0, M): one row each; its warps norm and rotate the q and k heads (sine and cosine of
-// the row's position are computed once per block, not per head) and write q and the cached k.
-// Blocks [M, M + tiles * nkv): a tile of VT_ROWS rows of one kv head's values, turned through
-// shared memory so that a warp writes 32 consecutive positions of one dimension (64 bytes in
-// bfloat16) instead of 32 scattered elements.  Every row's page and offset is looked up on its
-// own, so rows of different sequences or pages in one tile are fine.
+// A tile of VT_ROWS rows of one kv head's values, turned through shared memory so that a warp
+// writes 32 consecutive positions of one dimension (64 bytes in bfloat16) instead of 32
+// scattered elements.  Every row's page and offset is looked up on its own, so rows of
+// different sequences or pages in one tile are fine.
+template <typename T, typename CT>
+__device__ __forceinline__ void store_value_tile(
+    int t, const T* __restrict__ v_in, int kv_stride, CT* __restrict__ v_pool,
+    const int* __restrict__ block_table, int bt_width, const int* __restrict__ row_seq,
+    const int* __restrict__ row_pos, const int* __restrict__ seq_slot, int M, int nkv, int hd,
+    int page_size) {
+  constexpr int LD = VT_DIMS + (sizeof(CT) == 2 ? 2 : 1);     // odd number of 32-bit words
+  __shared__ CT tile[VT_ROWS * LD];
+  __shared__ long long dst[VT_ROWS];                          // element offset of (row, dim 0), or -1
+  const int kvh = t % nkv, m0 = (t / nkv) * VT_ROWS;
+  if (threadIdx.x < VT_ROWS) {
+    int m = m0 + threadIdx.x;
+    long long off = -1;
+    if (m < M) {
+      int b = row_seq[m], pos = row_pos[m];
+      if (seq_slot[b] >= 0) {
+        int page = block_table[(size_t)b * bt_width + pos / page_size];
+        if (page >= 0) off = ((long long)page * nkv + kvh) * hd * page_size + pos % page_size;
+      }
+    }
+    dst[threadIdx.x] = off;
+  }
+  for (int d0 = 0; d0 < hd; d0 += VT_DIMS) {
+    int nd = min(VT_DIMS, hd - d0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
+      int r = i / VT_DIMS, d = i % VT_DIMS;
+      if (d < nd && m0 + r < M)
+        tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]));
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
+      int d = i / VT_ROWS, r = i % VT_ROWS;
+      if (d < nd && dst[r] >= 0) v_pool[dst[r] + (size_t)(d0 + d) * page_size] = tile[r * LD + d];
+    }
+  }
+}
+
+// Blocks (x < M, y): row x, heads [8y, 8y + 8) of its q and k heads, one per warp: norm, rotate
+// (sine and cosine of the row's position are computed once per block, not per head), write q
+// and the cached k.  Blocks (x in [M, M + tiles * nkv), y = 0): a value tile.
 template <typename T, typename CT>
 __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     T* __restrict__ q_out, const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in,
@@ -39,38 +78,9 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
   pdl_wait();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if ((int)blockIdx.x >= M) {
-    // ---- value tile ----
-    CT* tile = reinterpret_cast<CT*>(sm);                       // [VT_ROWS][VT_DIMS + pad]
-    constexpr int LD = VT_DIMS + (sizeof(CT) == 2 ? 2 : 1);     // odd number of 32-bit words
-    __shared__ long long dst[VT_ROWS];                          // element offset of (row, dim 0), or -1
-    int t = blockIdx.x - M;
-    int kvh = t % nkv, m0 = (t / nkv) * VT_ROWS;
-    if (threadIdx.x < VT_ROWS) {
-      int m = m0 + threadIdx.x;
-      long long off = -1;
-      if (m < M) {
-        int b = row_seq[m], pos = row_pos[m];
-        if (seq_slot[b] >= 0) {
-          int page = block_table[(size_t)b * bt_width + pos / page_size];
-          if (page >= 0) off = ((long long)page * nkv + kvh) * hd * page_size + pos % page_size;
-        }
-      }
-      dst[threadIdx.x] = off;
-    }
-    for (int d0 = 0; d0 < hd; d0 += VT_DIMS) {
-      int nd = min(VT_DIMS, hd - d0);
-      __syncthreads();
-      for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
-        int r = i / VT_DIMS, d = i % VT_DIMS;
-        if (d < nd && m0 + r < M)
-          tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]));
-      }
-      __syncthreads();
-      for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
-        int d = i / VT_ROWS, r = i % VT_ROWS;
-        if (d < nd && dst[r] >= 0) v_pool[dst[r] + (size_t)(d0 + d) * page_size] = tile[r * LD + d];
-      }
-    }
+    if (blockIdx.y == 0)
+      store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
+                              seq_slot, M, nkv, hd, page_size);
     return;
   }
   // ---- one row: q and k heads ----
@@ -95,9 +105,10 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     int page = block_table[(size_t)b * bt_width + pos / page_size];
     if (page >= 0) kdst = ((long long)page * nkv * page_size + pos % page_size) * hd;
   }
-  for (int head = warp; head < total; head += ROPE_WARPS) {
+  int head = blockIdx.y * ROPE_WARPS + warp;
+  if (head < total) {
     bool is_q = head < nh;
-    if (!is_q && kdst < 0) continue;  // padding rows and positions outside a window own no cache
+    if (!is_q && kdst < 0) return;  // padding rows and positions outside a window own no cache
     const T* src = is_q ? q_in + (size_t)m * q_stride + (size_t)head * hd
                         : k_in + (size_t)m * kv_stride + (size_t)(head - nh) * hd;
     const float* nw = is_q ? q_norm_w : k_norm_w;
@@ -131,7 +142,100 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
       CT* o = k_pool + kdst + (size_t)(head - nh) * page_size * hd;
       for (int i = lane; i < hd; i += 32) o[i] = from_f32<CT>(v[i]);
     }
-    __syncwarp();
+  }
+}
+
+// The usual case (split-half pairing over the whole head, head size 64 or 128) without shared
+// memory: a lane holds elements lane, lane + 32, ... of a head, so both halves of a rotation
+// pair are in the same lane.  A warp takes `per_warp` consecutive heads of its row, four at a
+// time so that their loads are in flight together; sine and cosine are formed once per warp.
+// Same operations in the same order as the kernel above: the results are the same bit for bit.
+template <typename T, typename CT, int EPL>
+__global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_lanes_kernel(
+    T* __restrict__ q_out, const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in,
+    const T* __restrict__ v_in, int kv_stride, CT* __restrict__ k_pool, CT* __restrict__ v_pool,
+    const int* __restrict__ block_table, int bt_width,
+    const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp) {
+  constexpr int HD = EPL * 32, NP = EPL / 2, U = 4;
+  pdl_wait();
+  if ((int)blockIdx.x >= M) {
+    if (blockIdx.y == 0)
+      store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
+                              seq_slot, M, nkv, HD, page_size);
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int m = blockIdx.x;
+  const int total = nh + (k_in ? nkv : 0);
+  const int h0 = (blockIdx.y * ROPE_WARPS + warp) * per_warp;
+  if (h0 >= total) return;
+  const int h1 = min(h0 + per_warp, total);
+  const int b = row_seq[m], pos = row_pos[m];
+  long long kdst = -1;
+  if (h1 > nh && seq_slot[b] >= 0) {
+    const int page = block_table[(size_t)b * bt_width + pos / page_size];
+    if (page >= 0) kdst = ((long long)page * nkv * page_size + pos % page_size) * HD;
+  }
+  float c[NP], sn[NP], wq[EPL], wk[EPL];
+#pragma unroll
+  for (int p = 0; p < NP; p++) {
+    const float th = (float)pos * inv_freq[lane + 32 * p];
+    c[p] = cosf(th);
+    sn[p] = sinf(th);
+  }
+#pragma unroll
+  for (int e = 0; e < EPL; e++) {
+    wq[e] = q_norm_w ? q_norm_w[lane + 32 * e] : 1.f;
+    wk[e] = k_norm_w ? k_norm_w[lane + 32 * e] : 1.f;
+  }
+  for (int hb = h0; hb < h1; hb += U) {
+    float x[U][EPL];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int head = hb + u;
+      if (head < h1) {
+        const T* src = head < nh ? q_in + (size_t)m * q_stride + (size_t)head * HD
+                                 : k_in + (size_t)m * kv_stride + (size_t)(head - nh) * HD;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) x[u][e] = to_f32(src[lane + 32 * e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPL; e++) x[u][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int head = hb + u;
+      if (head >= h1) break;
+      const bool is_q = head < nh;
+      if (!is_q && kdst < 0) continue;
+      if (is_q ? q_norm_w != nullptr : k_norm_w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) ss += x[u][e] * x[u][e];
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int e = 0; e < EPL; e++) x[u][e] = x[u][e] * r * (is_q ? wq[e] : wk[e]);
+      }
+#pragma unroll
+      for (int p = 0; p < NP; p++) {
+        const float a = x[u][p], bb = x[u][p + NP];
+        x[u][p] = a * c[p] - bb * sn[p];
+        x[u][p + NP] = a * sn[p] + bb * c[p];
+      }
+      if (is_q) {
+        T* o = q_out + ((size_t)m * nh + head) * HD;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) o[lane + 32 * e] = from_f32<T>(x[u][e]);
+      } else {
+        CT* o = k_pool + kdst + (size_t)(head - nh) * page_size * HD;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) o[lane + 32 * e] = from_f32<CT>(x[u][e]);
+      }
+    }
   }
 }
 
@@ -146,9 +250,28 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
   LEB_REQUIRE(hd >= 2 && hd <= 512, "leb_qk_rope_store: head_dim %d outside 2..512", hd);
   LEB_REQUIRE(rope_dim <= hd && rope_dim % 2 == 0, "leb_qk_rope_store: rope_dim %d does not fit head_dim %d", rope_dim, hd);
   int tiles = k_in ? ceil_div(M, VT_ROWS) * nkv : 0;
-  dim3 grid(M + tiles), block(32 * ROPE_WARPS);
-  size_t smem = max((size_t)(rope_dim + ROPE_WARPS * hd) * sizeof(float),
-                    (size_t)VT_ROWS * (VT_DIMS + 2) * sizeof(float));
+  int total = nh + (k_in ? nkv : 0);
+  dim3 block(32 * ROPE_WARPS);
+  if (dtype == LEB_BF16 && inv_freq && neox && rope_dim == hd && (hd == 64 || hd == 128)) {
+    // heads per warp: one while the launch is small, up to all of a row's over 8 warps
+    int per_warp = 1;
+    while (per_warp * ROPE_WARPS < total && (long long)M * ceil_div(total, per_warp * ROPE_WARPS) > 4 * 148) per_warp++;
+    dim3 grid(M + tiles, ceil_div(total, per_warp * ROPE_WARPS));
+    if (hd == 64)
+      leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 2>, grid, block, 0, st,
+          (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
+          (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp);
+    else
+      leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 4>, grid, block, 0, st,
+          (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
+          (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp);
+    LEB_CHECK_LAUNCH("leb_qk_rope_store");
+    return 0;
+  }
+  dim3 grid(M + tiles, ceil_div(total, ROPE_WARPS));
+  size_t smem = (size_t)(rope_dim + ROPE_WARPS * hd) * sizeof(float);
   if (dtype == LEB_F32)
     leb_launch(qk_rope_store_kernel<float, float>, grid, block, smem, st,
         (float*)q_out, (const float*)q_in, q_stride, (const float*)k_in, (const float*)v_in,

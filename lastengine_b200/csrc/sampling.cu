@@ -258,6 +258,25 @@ __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_p
   seq_pos0[b] += 1;
 }
 
+// Before a decode step that was launched ahead of the host reading the previous step's choice:
+// sequence b takes as its token what the previous step chose for its place feed[b] there
+// (feed[b] < 0: the token the host staged stays).
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ chosen,
+                                   const int* __restrict__ feed, int B) {
+  pdl_wait();
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int f = feed[b];
+  if (f >= 0) tokens[b] = chosen[f];
+}
+
+LEB_API int leb_feed_tokens(int* tokens, const int* chosen, const int* feed, int B, cudaStream_t st) {
+  if (B <= 0) return 0;
+  leb_launch(feed_tokens_kernel, dim3(ceil_div(B, 128)), dim3(128), 0, st, tokens, chosen, feed, B);
+  LEB_CHECK_LAUNCH("leb_feed_tokens");
+  return 0;
+}
+
 LEB_API int leb_advance(int* tokens, int* row_pos, int* seq_pos0, const int* seq_slot,
                         const int* chosen, int B, cudaStream_t st) {
   if (B <= 0) return 0;

@@ -32,6 +32,7 @@ class StepBatch:
     n_logit_rows: int
     tables: dict[int, torch.Tensor] = field(default_factory=dict)   # kv group -> int32 [seqs, pages]
     u01: torch.Tensor | None = None   # float32 [seqs] uniform numbers for sampling
+    feed: torch.Tensor | None = None  # int32 [seqs] place in the previous step's choices to take the token from, or -1
     slots_host: list[int] = field(default_factory=list)
 
     @property
@@ -57,7 +58,7 @@ class BatchBuilder:
 
     def build(self, slots: list[int], tokens: list[list[int]] | list[np.ndarray], pos0: list[int],
               logit_rows: list[int], tables: dict[int, np.ndarray],
-              u01: np.ndarray | None = None, fixed: bool = False) -> StepBatch:
+              u01: np.ndarray | None = None, feed: np.ndarray | None = None) -> StepBatch:
         B = len(slots)
         qlen = np.fromiter((len(t) for t in tokens), dtype=np.int32, count=B)
         M = int(qlen.sum())
@@ -73,6 +74,8 @@ class BatchBuilder:
         tkeys = sorted(tables)
         if u01 is not None:
             pieces.append(np.asarray(u01, dtype=np.float32).view(np.int32))
+        if feed is not None:
+            pieces.append(np.asarray(feed, dtype=np.int32))
         n_head = len(pieces)      # the page tables come last: they change least often
         pieces += [np.ascontiguousarray(tables[k], dtype=np.int32).reshape(-1) for k in tkeys]
         # 4-int alignment keeps every piece 16-byte aligned
@@ -93,7 +96,8 @@ class BatchBuilder:
             self._copied.record()
         self.last_h2d_bytes = total * 4
         names = ["tokens", "row_seq", "row_pos", "seq_slot", "seq_pos0", "seq_qstart", "seq_qlen", "logit_rows"]
-        names += (["u01"] if u01 is not None else []) + [f"table{k}" for k in tkeys]
+        names += (["u01"] if u01 is not None else []) + (["feed"] if feed is not None else [])
+        names += [f"table{k}" for k in tkeys]
         self.layout = {n: (o, p.size) for n, o, p in zip(names, offs, pieces)}
         self.total = total
         self.head_total = offs[n_head] if tkeys else total     # everything before the page tables
@@ -106,12 +110,13 @@ class BatchBuilder:
         for j, k in enumerate(tkeys):
             tabs[k] = piece(n_head + j).view(B, -1)
         u = piece(8).view(torch.float32) if u01 is not None else None
+        fd = piece(8 + (u01 is not None)) if feed is not None else None
         return StepBatch(
             n_rows=M, n_seqs=B, max_qlen=int(qlen.max()) if B else 0,
             max_kvlen=int((pos0a + qlen).max()) if B else 0,
             tokens=piece(0), row_seq=piece(1), row_pos=piece(2), seq_slot=piece(3), seq_pos0=piece(4),
             seq_qstart=piece(5), seq_qlen=piece(6), logit_rows=piece(7), n_logit_rows=int(lr.size),
-            tables=tabs, u01=u, slots_host=list(slots))
+            tables=tabs, u01=u, feed=fd, slots_host=list(slots))
 
     # ---- the same step again, one position later -----------------------------------------------
     def host_view(self, name: str) -> np.ndarray:

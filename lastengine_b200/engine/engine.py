@@ -103,7 +103,7 @@ class Engine:
     def prepare(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
                 want: str | Sequence[Sequence[int]] | None = "last",
                 u01: np.ndarray | None = None, builder: BatchBuilder | None = None,
-                table_width: int | None = None) -> tuple[StepBatch, dict[int, int]]:
+                table_width: int | None = None, feed: np.ndarray | None = None) -> tuple[StepBatch, dict[int, int]]:
         """Checks a step, reserves its cache room and lays it out on the device."""
         if not self.loaded:
             raise RuntimeError("the engine has no weights yet")
@@ -152,7 +152,7 @@ class Engine:
         for gi, g in enumerate(self.cache.kv_groups):
             width = table_width or max(1, max((len(g.seq_pages.get(s, ())) for s in live), default=1))
             tables[gi] = g.table(list(seqs), width)
-        b = (builder or self.builder).build(list(seqs), tokens, pos0, rows, tables, u01=u01)
+        b = (builder or self.builder).build(list(seqs), tokens, pos0, rows, tables, u01=u01, feed=feed)
         return b, grow
 
     def step(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],

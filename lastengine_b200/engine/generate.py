@@ -54,7 +54,10 @@ class Backend(Protocol):
 
     def decode(self, slots: list[int], tokens: list[int], u01: list[float] | None,
                histories: list[list[int]]) -> list[int]:
-        """Feeds one token per slot; returns the next token of each."""
+        """Feeds one token per slot; returns the next token of each.  A backend with a true
+        attribute `lookahead` also takes `lookahead=(the following step's uniform numbers or
+        None, for each slot whether its request can go on after this step)`, a promise that the
+        next call feeds the returned tokens to a subset of those slots; it may run ahead on it."""
 
     def finish(self, slots: list[int]) -> None:
         """Gives the slots back."""
@@ -157,8 +160,12 @@ class GenerationLoop:
                 if not active:
                     break
                 u = [r.rng.next() for r in active] if draw else None
+                kw = {}
+                if getattr(self.backend, "lookahead", False):
+                    kw["lookahead"] = ([r.rng.peek() for r in active] if draw else None,
+                                       [len(r.out) + 1 < r.budget for r in active])
                 toks = self.backend.decode([r.slot for r in active], [r.out[-1] for r in active], u,
-                                           [r.history for r in active] if want_hist else None)
+                                           [r.history for r in active] if want_hist else None, **kw)
                 stats.decode_steps += 1
                 stats.decode_tokens += len(active)
             stats.decode_ms += (self.clock() - t1) * 1e3

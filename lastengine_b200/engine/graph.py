@@ -13,6 +13,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from ..cache import CacheFull
 from ..ops import kernels
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -34,12 +35,16 @@ class DecodeGraph:
     """The captured step of one bucket: forward pass, choice of the next tokens, and (for runs
     that feed themselves) the move to the next position."""
 
-    def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False):
+    def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False,
+                 out: torch.Tensor | None = None, fed: bool = False):
+        """`out`: where the chosen tokens go (shared between the buckets of one backend, so that a
+        step of one bucket can take its tokens from the step of another).  `fed`: the step begins
+        by taking tokens from `out` where the staged step says so."""
         self.engine, self.sampler, self.bucket, self.width = engine, sampler, bucket, table_width
-        self.self_feeding = self_feeding
+        self.self_feeding, self.fed = self_feeding, fed
         self.ws = Workspace(engine.device)
         self.builder = BatchBuilder(engine.device)
-        self.out = torch.zeros(bucket, dtype=torch.int32, device=engine.device)
+        self.out = out if out is not None else torch.zeros(bucket, dtype=torch.int32, device=engine.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.batch = None
         self.staged_slots: list[int] = []
@@ -48,22 +53,30 @@ class DecodeGraph:
 
     def _run(self, batch) -> None:
         eng = self.engine
+        if batch.feed is not None:
+            kernels.feed_tokens(batch, self.out)
         logits = eng.model.forward(batch, eng.cache)
-        self.sampler.sample(self.out, logits, batch.u01)
+        self.sampler.sample(self.out[:self.bucket], logits, batch.u01)
         if self.self_feeding:
             kernels.advance(batch, self.out)
 
-    def stage(self, slots: list[int], tokens: list[int], u01) -> dict[int, int]:
-        """Lays the step's inputs out in this bucket's fixed device buffers (one copy)."""
+    def stage(self, slots: list[int], tokens: list[int] | None, u01, feed=None) -> dict[int, int]:
+        """Lays the step's inputs out in this bucket's fixed device buffers (one copy).  With
+        `feed`, sequence i takes the token the previous step chose at place feed[i]."""
         eng = self.engine
         pad = self.bucket - len(slots)
         seqs = list(slots) + [-1] * pad
-        toks = [[t] for t in tokens] + [[0]] * pad
+        toks = [[t] for t in (tokens if tokens is not None else [0] * len(slots))] + [[0]] * pad
         u = None
         if self.sampler.needs_uniform():
             u = np.zeros(self.bucket, dtype=np.float32)
             u[:len(slots)] = u01
-        batch, grow = eng.prepare(seqs, toks, "last", u01=u, builder=self.builder, table_width=self.width)
+        fd = None
+        if self.fed:
+            fd = np.full(self.bucket, -1, dtype=np.int32)
+            if feed is not None:
+                fd[:len(slots)] = feed
+        batch, grow = eng.prepare(seqs, toks, "last", u01=u, builder=self.builder, table_width=self.width, feed=fd)
         if self.batch is not None:
             same = (batch.tokens.data_ptr() == self.batch.tokens.data_ptr()
                     and all(batch.tables[k].data_ptr() == self.batch.tables[k].data_ptr() for k in batch.tables))
@@ -75,7 +88,7 @@ class DecodeGraph:
         self.staged_slots = list(slots)
         return grow
 
-    def restage(self, slots: list[int], tokens: list[int], u01) -> dict[int, int] | None:
+    def restage(self, slots: list[int], tokens: list[int] | None, u01, feed=None) -> dict[int, int] | None:
         """The step after the one staged before, for the same sequences in the same order: only
         the tokens, the positions (+1) and, where a sequence enters a new page, one entry of its
         page table change.  Done in place in the staging buffer, then one copy.  Returns None
@@ -102,7 +115,10 @@ class DecodeGraph:
                     if len(lst) > tab.shape[1]:
                         return None
                     tab[i, len(lst) - 1] = lst[-1]
-        bb.host_view("tokens")[:n] = tokens
+        if tokens is not None:
+            bb.host_view("tokens")[:n] = tokens
+        if "feed" in bb.layout:
+            bb.host_view("feed")[:n] = feed if feed is not None else -1
         pos[:n] += 1
         bb.host_view("row_pos")[:n] += 1
         if u01 is not None and "u01" in bb.layout:
@@ -137,8 +153,27 @@ class DecodeGraph:
             eng.env.workspace = saved
 
 
+class _StepInFlight:
+    """A launched decode step whose chosen tokens the host has not read yet."""
+
+    def __init__(self, number: int, slots: list[int], host: torch.Tensor, event: torch.cuda.Event):
+        self.number, self.slots, self.host, self.event = number, slots, host, event
+
+
 class GraphBackend(EngineBackend):
-    """The generation loop's backend with graph-replayed decode steps."""
+    """The generation loop's backend with graph-replayed decode steps, launched one step ahead.
+
+    While the device runs step k the host has nothing to do but wait, and after it the device
+    would wait for the host to read the tokens, decide and stage step k+1.  So when the loop
+    says which requests can go on after step k (`lookahead`), step k+1 is launched for them
+    before step k's tokens are read: it takes its tokens from step k's choices on the device.
+    A request that step k ends with a stop token has then run one step too many; its row is
+    dropped, and its slot is given back only after that step has finished, since the step
+    still writes to its pages.  Rows do not depend on each other, so the other requests'
+    tokens are those they would have got without it.
+    """
+
+    lookahead = True
 
     def __init__(self, engine, sampling: SamplingParams, max_batch: int = 64, max_seq_len: int | None = None):
         super().__init__(engine, sampling)
@@ -147,26 +182,112 @@ class GraphBackend(EngineBackend):
         # Captured graphs outlive one call: they belong to the engine, keyed by what is baked into
         # them (the sampling constants and the width of the page tables).
         store = engine.__dict__.setdefault("_decode_graphs", {})
-        self.graphs: dict[int, DecodeGraph] = store.setdefault((sampling, self.width), {})
+        self.graphs: dict = store.setdefault((sampling, self.width), {})
         self.h2d_bytes = 0
+        self._ahead: _StepInFlight | None = None
+        self._launched = 0
+        self._held: list[tuple[int, list[int]]] = []     # (step number to wait for, slots to give back)
+        self._fed: dict[int, int] = {}                    # slot -> the token the next step was given on the device
 
-    def decode(self, slots, tokens, u01, histories):
-        if self.sampler.params.has_penalties:
-            return super().decode(slots, tokens, u01, histories)
+    def _chosen(self, n: int) -> torch.Tensor:
+        out = self.graphs.get("out")
+        if out is None or out.numel() < n:
+            # graphs point at the old buffer: they are captured again with the new one
+            for k in [k for k in self.graphs if k != "out"]:
+                del self.graphs[k]
+            out = self.graphs["out"] = torch.zeros(max(256, n), dtype=torch.int32, device=self.engine.device)
+        return out
+
+    def _launch(self, slots, tokens, u01, feed) -> _StepInFlight:
         eng = self.engine
         b = bucket_for(len(slots))
+        out = self._chosen(b)
         g = self.graphs.get(b)
         if g is None:
-            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width)
-        grow = g.restage(slots, tokens, u01)
+            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width, out=out, fed=True)
+        grow = g.restage(slots, tokens, u01, feed)
         if grow is None:
-            grow = g.stage(slots, tokens, u01)
+            grow = g.stage(slots, tokens, u01, feed)
         g.launch()
         eng.cache.commit(grow)
         g.cache_version = eng.cache.state_version
         n = len(slots)
-        self._host[:n].copy_(g.out[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._launched += 1
+        host = torch.empty(n, dtype=torch.int32, pin_memory=True) if n > 1024 else \
+            self._hosts[self._launched % 2]
+        host[:n].copy_(out[:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
         self.h2d_bytes = g.builder.last_h2d_bytes
         self.d2h_bytes = n * 4
-        return self._host[:n].tolist()
+        return _StepInFlight(self._launched, list(slots), host, ev)
+
+    @property
+    def _hosts(self):
+        h = self.__dict__.get("_host_pair")
+        if h is None:
+            h = self.__dict__["_host_pair"] = [torch.empty(1024, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        return h
+
+    def _wait(self, step: _StepInFlight) -> list[int]:
+        step.event.synchronize()
+        toks = step.host[:len(step.slots)].tolist()
+        still = []
+        for number, slots in self._held:
+            if number <= step.number:
+                self.engine.release(slots)
+            else:
+                still.append((number, slots))
+        self._held = still
+        return toks
+
+    def _drain(self) -> None:
+        if self._ahead is not None:
+            self._wait(self._ahead)
+            self._ahead = None
+        self._fed = {}
+
+    def start(self, prompts, u01, histories):
+        self._drain()
+        return super().start(prompts, u01, histories)
+
+    def finish(self, slots):
+        if self._ahead is None:
+            self.engine.release(slots)
+            return
+        self._held.append((self._ahead.number, list(slots)))
+        gone = {s for _, ss in self._held for s in ss}
+        if all(s in gone for s in self._ahead.slots):
+            self._drain()          # nothing of the step ahead is wanted any more
+
+    def decode(self, slots, tokens, u01, histories, lookahead=None):
+        """`lookahead` = (the uniform numbers of the step after this one or None, for each slot
+        whether its request can go on after this step's token)."""
+        if self.sampler.params.has_penalties:
+            self._drain()
+            return super().decode(slots, tokens, u01, histories)
+        step, self._ahead = self._ahead, None
+        if step is not None:
+            place = {s: i for i, s in enumerate(step.slots)}
+            if any(s not in place or self._fed.get(s) != t for s, t in zip(slots, tokens)):
+                self._wait(step)
+                raise RuntimeError("decode was asked for a step other than the one launched ahead "
+                                   "(a request that was said to end goes on, or a token other than the chosen one is fed)")
+            pick = [place[s] for s in slots]
+        else:
+            step = self._launch(slots, tokens, u01, None)
+            pick = list(range(len(slots)))
+        if lookahead is not None:
+            next_u01, goes_on = lookahead
+            keep = [i for i, c in enumerate(goes_on) if c]
+            if keep and (next_u01 is not None or not self.sampler.needs_uniform()):
+                try:
+                    self._ahead = self._launch([slots[i] for i in keep], None,
+                                               [next_u01[i] for i in keep] if next_u01 is not None else None,
+                                               [pick[i] for i in keep])
+                except CacheFull:
+                    self._ahead = None      # no room to run ahead: the next step is staged when it is asked for
+        toks = self._wait(step)
+        res = [toks[i] for i in pick]
+        self._fed = dict(zip(slots, res)) if self._ahead is not None else {}
+        return res

@@ -48,6 +48,7 @@ def _declare(L) -> None:
         "leb_argmax": [P, P, I, I, P],
         "leb_sample": [P, P, P, I, I, I, F, F, F, P],
         "leb_advance": [P, P, P, P, P, I, P],
+        "leb_feed_tokens": [P, P, P, I, P],
         "leb_attention_decode_supported": [I, I, I, I],
         "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
@@ -222,15 +223,26 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
 def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
     """How many blocks share one sequence's key range in a decode step (1 for prompts).
 
-    Measured on B200 (head size 64, 8 kv heads): about 1024 positions per block is best at any
-    batch size, and with few sequences more splits are worth it until some 128 blocks run.
+    Measured on B200 (head size 64, 8 kv heads): about 1024 positions per block is best with many
+    sequences, with few sequences more splits are worth it until some 128 blocks run, and a
+    split count that needs one more wave of blocks than the GPU holds at once (two per SM) costs
+    more than it saves.  The count with the least (waves x positions per block, in units of 32)
+    plus half a unit per split (and per wave of
+    rows) for the merge is taken; a block gets at least 128 positions.
     """
     if batch.max_qlen != 1:
         return 1
     kv = max(int(batch.max_kvlen), 1)
-    per = batch.n_seqs * nkv * ((G + 15) // 16)
-    want = max(-(-kv // 1024), -(-128 // max(per, 1)))
-    return max(1, min(32, want, -(-kv // 128)))
+    per = max(batch.n_seqs * nkv * ((G + 15) // 16), 1)
+    best, best_cost = 1, None
+    for n in range(1, 33):
+        each = -(-kv // n)
+        if n > 1 and each < 128:
+            break
+        cost = -(-per * n // (2 * sm_count)) * -(-each // 32) + 0.5 * n * max(1.0, per / (2 * sm_count))
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return best
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -465,6 +477,12 @@ def advance(batch, chosen: torch.Tensor) -> None:
     _cuda(chosen, "advance.chosen", torch.int32)
     _check(lib().leb_advance(_ptr(batch.tokens), _ptr(batch.row_pos), _ptr(batch.seq_pos0), _ptr(batch.seq_slot),
                              _ptr(chosen), batch.n_seqs, _stream()))
+
+
+def feed_tokens(batch, chosen: torch.Tensor) -> None:
+    """Sequences with batch.feed[b] >= 0 take as their token what `chosen` holds at that place."""
+    _cuda(chosen, "feed_tokens.chosen", torch.int32)
+    _check(lib().leb_feed_tokens(_ptr(batch.tokens), _ptr(chosen), _ptr(batch.feed), batch.n_seqs, _stream()))
 
 
 def launch_count() -> int:

@@ -47,10 +47,17 @@ class XorShift64:
         s = (seed if seed is not None else 1) + stream
         self.state = ((s * GOLDEN) & MASK64) | 1
 
-    def next(self) -> float:
-        s = self.state
+    @staticmethod
+    def _advance(s: int) -> int:
         s ^= (s << 13) & MASK64
         s ^= s >> 7
         s ^= (s << 17) & MASK64
-        self.state = s
-        return (s >> 40) / float(1 << 24)
+        return s
+
+    def next(self) -> float:
+        self.state = self._advance(self.state)
+        return (self.state >> 40) / float(1 << 24)
+
+    def peek(self) -> float:
+        """The number the next call of `next` will give; the state stays."""
+        return (self._advance(self.state) >> 40) / float(1 << 24)

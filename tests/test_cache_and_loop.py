@@ -210,6 +210,49 @@ def test_loop_builds_histories_only_for_penalties():
     assert seen and seen[0] == [[0, 5, 1]]
 
 
+class LookingAhead(Scripted):
+    """A scripted backend that takes the loop's look-ahead and checks that the loop keeps it."""
+    lookahead = True
+
+    def __init__(self, script):
+        super().__init__(script)
+        self.promised = None
+
+    def decode(self, slots, tokens, u01, histories, lookahead=None):
+        if self.promised is not None:
+            next_u, may, given = self.promised
+            assert set(slots) <= may                                   # only requests said to go on come back
+            assert all(given[s] == t for s, t in zip(slots, tokens))   # and they are fed what was chosen
+            if next_u is not None:
+                assert [next_u[s] for s in slots] == u01
+        res = super().decode(slots, tokens, u01, histories)
+        assert lookahead is not None
+        nu, goes_on = lookahead
+        self.promised = (dict(zip(slots, nu)) if nu is not None else None,
+                         {s for s, c in zip(slots, goes_on) if c}, dict(zip(slots, res)))
+        return res
+
+    def start(self, prompts, u01, histories):
+        self.promised = None
+        return super().start(prompts, u01, histories)
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_loop_look_ahead_is_a_promise_it_keeps(temperature):
+    script = {0: [5, 6, 99, 7], 1: [99], 2: [1, 2, 3, 4, 5, 6], 3: [8, 8, 8, 8, 8, 8], 4: [9, 99]}
+    be = LookingAhead(script)
+    loop = GenerationLoop(be, SamplingParams(temperature=temperature, seed=3), max_new_tokens=4, stop_token_ids=[99], max_batch=3)
+    res = loop.run([[0, 50], [1], [2, 50, 51], [3], [4, 1, 2, 3]])
+    assert res.tokens == [[5, 6], [], [1, 2, 3, 4], [8, 8, 8, 8], [9]]
+    plain = Scripted(script)
+    res2 = GenerationLoop(plain, SamplingParams(temperature=temperature, seed=3), max_new_tokens=4, stop_token_ids=[99],
+                          max_batch=3).run([[0, 50], [1], [2, 50, 51], [3], [4, 1, 2, 3]])
+    assert res2.tokens == res.tokens and plain.log == be.log          # the same calls with the same numbers
+    g = XorShift64(5)
+    a = g.peek()
+    assert a == g.next() and g.peek() != a
+
+
 def test_plan_batches_respects_cache_room():
     assert plan_batches([10, 10, 10], [5, 5, 5], max_batch=2, token_budget=1000, page=64) == [[0, 1], [2]]
     assert plan_batches([60, 60, 60], [10, 10, 10], max_batch=8, token_budget=256, page=64) == [[0, 1], [2]]

@@ -91,6 +91,13 @@ def test_stop_tokens_end_requests_early(dirs):
         assert r == f[:cut]                      # the stop token is not part of the output
         assert reason == ("stop" if stop in f else "length")
     assert eng.cache.slots.n_held == 0
+    eng.cache.check()
+    # steps launched ahead of the host (graphs) and steps run one by one give the same tokens
+    slow = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=10, stop_token_ids=[stop], use_graphs=False)
+    assert slow.tokens == res.tokens and slow.finish_reasons == res.finish_reasons
+    sp = SamplingParams(temperature=0.9, seed=5)
+    assert eng.generate(prompts, sp, max_new_tokens=10, stop_token_ids=[stop]).tokens == \
+        eng.generate(prompts, sp, max_new_tokens=10, stop_token_ids=[stop], use_graphs=False).tokens
 
 
 def run_trace(model_dir, dtype, steps, out_dir, max_tokens=1024):

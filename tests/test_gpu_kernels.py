@@ -210,18 +210,26 @@ def test_shortconv_many_rows(Lc, D):
 
 # ---- rotation and cache write ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,rope_dim", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80)])
-def test_qk_rope_store(dtype, nh, nkv, hd, rope_dim):
+@pytest.mark.parametrize("nh,nkv,hd,rope_dim,lens", [(4, 2, 16, 16, [3, 70]), (3, 1, 48, 32, [3, 70]), (5, 5, 80, 80, [3, 70]),
+                                                      (2, 1, 64, 64, [3, 70]), (6, 2, 128, 128, [3, 70]),
+                                                      (9, 3, 64, 64, [60, 100]), (13, 1, 64, 64, [400, 290])])
+def test_qk_rope_store(dtype, nh, nkv, hd, rope_dim, lens):
+    if dtype == torch.float32 and max(lens) > 128:
+        # a float angle is off by up to position x 6e-8: the float path is compared at short positions
+        # only; the long case is there for the bfloat16 kernel that takes several heads per warp
+        lens = [n // 4 for n in lens]
     page = 64
-    lens, pos0 = [3, 70], [62, 5]                   # rows cross a page boundary
+    pos0 = [62, 5]                                  # rows cross a page boundary
     M = sum(lens)
     width = nh * hd + 2 * nkv * hd
     qkv = gen(M, width, seed=30, dtype=dtype)
     qn, kn = 1 + 0.1 * gen(hd, seed=31), 1 + 0.1 * gen(hd, seed=32)
     theta, eps = 12345.0, 1e-4
     inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rope_dim // 2, dtype=torch.float64) / rope_dim).float()
-    n_pages = 8
-    tables = {0: np.array([[5, 2, -1], [1, 7, 3]], dtype=np.int32)}
+    width = max(-(-(p + n) // page) for p, n in zip(pos0, lens))
+    n_pages = 2 * width + 2
+    order = np.random.default_rng(5).permutation(n_pages)[:2 * width].astype(np.int32)   # pages in no order
+    tables = {0: order.reshape(2, width)}
     kp = torch.zeros(n_pages, nkv, page, hd, device=DEV, dtype=dtype)
     vp = torch.zeros(n_pages, nkv, hd, page, device=DEV, dtype=dtype)      # values: positions contiguous
     batch = builder().build([0, 1], [[0] * n for n in lens], pos0, [], tables)
