@@ -1,0 +1,234 @@
+// bfloat16 matrix product for up to 16 rows (the decode step):  C[M,N] (+)= A[M,K] . W[N,K]^T,
+// float accumulate, built as a pipelined stream of the weights through shared memory.
+//
+// Such a product is bound by reading W once (the reference's decode matvec is one pass over the
+// weight rows too, src/cuda/kernels.cu:371-392), and a stream is only as fast as the bytes it
+// keeps in flight.  Registers hold too few: a warp that loads a batch of weights, waits and
+// multiplies pays the memory latency once per batch.  Here every warp owns a ring of S stages in
+// shared memory and keeps S-1 asynchronous copies (cp.async, 16 bytes per lane, straight from
+// L2 to shared memory) in flight at all times; the weight copies of the first stages are issued
+// before the kernel waits for its predecessor, since weights do not depend on it.  A stage
+// holds the activations of its 64 values of k as well, so nothing in the loop waits on a load.
+//
+// A block owns tiles of 16*NSUB weight rows; its NW warps split K in chunks of 64 (warp w takes
+// chunks w, w+NW, ...) and their partial sums are added in warp order through shared memory, so
+// a row's result does not depend on the other rows of the launch.  Blocks are persistent:
+// block b takes tiles b, b+grid, ... and its rings run on across tiles, so there is no bubble
+// between them.  The tensor-core roles are swapped as in the register kernel: 16 weight rows
+// are the "M" side of mma.m16n8k16, 8 activation rows its "N" side, and a lane's 16 bytes
+// (8 values of k) feed two mma as k-pairs (0,1)(2,3) and (4,5)(6,7) on both operands.
+//
+// A stage holds rows of 128 bytes; the 16-byte piece c of row r lies at c ^ 4*(r & 1), so the
+// quarter-warps of a 16-byte shared load (rows 2i and 2i+1, four pieces each) hit all 32 banks.
+//
+// epilogue: 0 store, 1 add into float C, 2 SwiGLU over interleaved weights (rows 32j..32j+15
+// gate, 32j+16..32j+31 up of the same 16 outputs; C has N/2 columns).
+#include "common.cuh"
+
+#define ST_ROWS 16
+#define ST_CHUNK 64
+
+__device__ __forceinline__ void st_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void st_cp16(uint32_t dst, const void* src, int bytes) {
+  // copies `bytes` (16 or 0) and fills the rest of the 16 with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void st_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 st_lds(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
+__global__ void __launch_bounds__(32 * ST_WARPS)
+gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
+                        int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles) {
+  constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
+  extern __shared__ __align__(128) unsigned char st_smem[];
+  float (*red)[NSUB][ST_ROWS][8 * MT + 1] =
+      reinterpret_cast<float (*)[NSUB][ST_ROWS][8 * MT + 1]>(st_smem + (size_t)ST_WARPS * S * STAGE);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(st_smem) + warp * (S * STAGE);
+  const int n_chunks = (K + ST_CHUNK - 1) / ST_CHUNK;
+  const int my_chunks = warp < n_chunks ? (n_chunks - warp + ST_WARPS - 1) / ST_WARPS : 0;
+  const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int total = my_tiles * my_chunks;   // this warp's stages, tile after tile
+
+  // producer state: the next stage to ask for
+  int p_q = 0, p_tile = blockIdx.x, p_ci = 0;
+  auto issue_x = [&](int q, int ci) {   // the activations of stage q (chunk ci of this warp)
+    const int k0 = (warp + ST_WARPS * ci) * ST_CHUNK;
+    const uint32_t base = ring + (q % S) * STAGE + XOFF;
+#pragma unroll
+    for (int i = 0; i < 2 * MT; i++) {
+      const int row = i * 4 + (lane >> 3), ch = lane & 7;
+      const int k = k0 + ch * 8;
+      const bool in = row < M && k < K;
+      st_cp16(base + row * 128 + ((ch ^ ((row & 1) << 2)) << 4), A + (in ? (size_t)row * lda + k : 0), in ? 16 : 0);
+    }
+  };
+  auto issue = [&](bool with_x) {
+    if (p_q < total) {
+      const int k0 = (warp + ST_WARPS * p_ci) * ST_CHUNK, n0 = p_tile * ROWS;
+      const uint32_t base = ring + (p_q % S) * STAGE;
+      if (with_x) issue_x(p_q, p_ci);
+#pragma unroll
+      for (int i = 0; i < ROWS / 4; i++) {
+        const int row = i * 4 + (lane >> 3), ch = lane & 7;
+        const int n = min(n0 + row, N - 1), k = k0 + ch * 8;
+        const bool in = k < K;   // K is a multiple of 8: a piece is inside or outside as a whole
+        st_cp16(base + row * 128 + ((ch ^ ((row & 1) << 2)) << 4), W + (size_t)n * K + (in ? k : 0), in ? 16 : 0);
+      }
+      p_q++;
+      if (++p_ci == my_chunks) {
+        p_ci = 0;
+        p_tile += gridDim.x;
+      }
+    }
+    st_commit();   // an empty group where there is nothing left: the count of groups stays in step
+  };
+#pragma unroll
+  for (int i = 0; i < S - 1; i++) issue(false);
+  pdl_wait();
+  // the activations of those first stages, in one more group (stage i is chunk i % my_chunks)
+#pragma unroll
+  for (int i = 0; i < S - 1; i++)
+    if (i < total) issue_x(i, i % my_chunks);
+  st_commit();
+  int q = 0;
+  for (int ti = 0; ti < my_tiles; ti++) {
+    const int tile = blockIdx.x + ti * gridDim.x;
+    float acc[NSUB][MT][4];
+#pragma unroll
+    for (int s = 0; s < NSUB; s++)
+#pragma unroll
+      for (int t = 0; t < MT; t++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[s][t][e] = 0.f;
+    for (int ci = 0; ci < my_chunks; ci++, q++) {
+      // the first stages' activations came in one group after all their weights: wait for all
+      if (q == 0) st_wait<0>(); else st_wait<S - 2>();
+      __syncwarp();      // every lane's copies of stage q have landed; everyone is done with stage q-1
+      issue(true);       // refills the slot of stage q-1
+      const uint32_t base = ring + (q % S) * STAGE;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const uint32_t off = g * 128 + (((4 * j + t4) ^ ((g & 1) << 2)) << 4);
+        uint4 xc[MT];
+#pragma unroll
+        for (int t = 0; t < MT; t++) xc[t] = st_lds(base + XOFF + t * 8 * 128 + off);
+#pragma unroll
+        for (int s = 0; s < NSUB; s++) {
+          const uint4 w0 = st_lds(base + s * ST_ROWS * 128 + off), w1 = st_lds(base + s * ST_ROWS * 128 + off + 8 * 128);
+#pragma unroll
+          for (int t = 0; t < MT; t++) {
+            st_mma(acc[s][t], w0.x, w1.x, w0.y, w1.y, xc[t].x, xc[t].y);
+            st_mma(acc[s][t], w0.z, w1.z, w0.w, w1.w, xc[t].z, xc[t].w);
+          }
+        }
+      }
+    }
+    // accumulator fragment: [0] (row g, col 2 t4) [1] (g, 2 t4 + 1) [2] (g + 8, 2 t4) [3] (g + 8, 2 t4 + 1)
+#pragma unroll
+    for (int s = 0; s < NSUB; s++)
+#pragma unroll
+      for (int t = 0; t < MT; t++) {
+        red[warp][s][g][t * 8 + 2 * t4] = acc[s][t][0];
+        red[warp][s][g][t * 8 + 2 * t4 + 1] = acc[s][t][1];
+        red[warp][s][g + 8][t * 8 + 2 * t4] = acc[s][t][2];
+        red[warp][s][g + 8][t * 8 + 2 * t4 + 1] = acc[s][t][3];
+      }
+    __syncthreads();
+    if (epilogue == 2) {
+      // NSUB == 2: sub-tile 0 holds the gate rows, sub-tile 1 the up rows of outputs 16 * tile + i
+      const int jbase = tile * ST_ROWS;
+      for (int idx = threadIdx.x; idx < ST_ROWS * 8 * MT; idx += blockDim.x) {
+        const int col = idx / ST_ROWS, i = idx % ST_ROWS;   // consecutive threads: consecutive outputs
+        if (col >= M || 2 * (jbase + i) >= N) continue;
+        float gt = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS; w++) {
+          gt += red[w][0][i][col];
+          up += red[w][NSUB - 1][i][col];
+        }
+        C[(size_t)col * ldc + jbase + i] = from_f32<TC>(gt / (1.0f + expf(-gt)) * up);
+      }
+    } else {
+      const int n0 = tile * ROWS;
+      for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {
+        const int col = idx / ROWS, rr = idx % ROWS;
+        const int n = n0 + rr;
+        if (col >= M || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS; w++) v += red[w][rr / ST_ROWS][rr % ST_ROWS][col];
+        TC* cp = C + (size_t)col * ldc + n;
+        if (epilogue == 1) v += to_f32(*cp);
+        *cp = from_f32<TC>(v);
+      }
+    }
+    __syncthreads();   // the sums are read before the next tile's are written
+  }
+  st_wait<0>();
+}
+
+template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
+static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, int K, int lda, int ldc,
+                         int epilogue, cudaStream_t st) {
+  constexpr int ROWS = ST_ROWS * NSUB;
+  constexpr size_t smem = (size_t)ST_WARPS * S * (ROWS + 8 * MT) * 128 + sizeof(float) * ST_WARPS * NSUB * ST_ROWS * (8 * MT + 1);
+  static int slots = 0;   // blocks the GPU holds at once
+  if (!slots) {
+    int dev = 0, n_sm = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaFuncSetAttribute(gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return leb_fail("leb_gemm_bf16_stream: %zu bytes of shared memory per block refused", smem);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, 32 * ST_WARPS, smem);
+    slots = max(1, per_sm) * max(1, n_sm);
+  }
+  const int n_tiles = ceil_div(N, ROWS);
+  // the same number of tiles for every block (as far as it goes), all blocks on the GPU at once
+  const int per_block = ceil_div(n_tiles, slots);
+  const int grid = ceil_div(n_tiles, per_block);
+  leb_launch(gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st, (TC*)C, A, W, M, N,
+             K, lda, ldc, epilogue, n_tiles);
+  LEB_CHECK_LAUNCH("leb_gemm_bf16_stream");
+  return 0;
+}
+
+template <typename TC>
+static int stream_dispatch(void* C, const bf16* a, const bf16* w, int M, int N, int K, int lda, int ldc, int epilogue,
+                           cudaStream_t st) {
+  if (epilogue == 2) {
+    if (M <= 8) return launch_stream<TC, 1, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+    return launch_stream<TC, 2, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+  }
+  if (M <= 8) return launch_stream<TC, 1, 1, 4, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+  return launch_stream<TC, 2, 1, 3, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+}
+
+LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
+                                 int ldc, int epilogue, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream: %d rows; this kernel takes at most 16", M);
+  LEB_REQUIRE(K > 0 && K % 8 == 0, "leb_gemm_bf16_stream: K (%d) must be a multiple of 8", K);
+  LEB_REQUIRE(lda % 8 == 0, "leb_gemm_bf16_stream: row stride of A (%d) must be a multiple of 8", lda);
+  LEB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "leb_gemm_bf16_stream: A and W must be 16-byte aligned");
+  LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_stream: unknown epilogue %d", epilogue);
+  LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_stream: adding needs a float C");
+  LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_stream: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
+  if (c_dtype == LEB_BF16) return stream_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
+  if (c_dtype == LEB_F32) return stream_dispatch<float>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
+  return leb_fail("leb_gemm_bf16_stream: unknown C dtype %d", c_dtype);
+}

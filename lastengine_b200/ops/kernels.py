@@ -40,6 +40,7 @@ def _declare(L) -> None:
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
+        "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
         "leb_gemm_bf16_small_norm": [P, I, P, I, P, F, P, I, I, I, I, I, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
         "leb_moe_align": [P, P, P, P, I, I, P],
@@ -337,8 +338,9 @@ def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
     float32 operands run on the CUDA cores in true 32-bit; bfloat16 operands on the tensor
     cores with float accumulation.  `epilogue`: STORE, ACCUMULATE (out is the float residual)
     or SWIGLU (w holds gate and up rows interleaved in blocks of 16; out has N/2 columns).
-    With more than SMALL_M rows bfloat16 products go to the tcgen05 kernel, unless `streaming`
-    asks for the weight-streaming kernel whatever the row count.
+    Up to SMALL_M rows bfloat16 products stream W through shared memory with asynchronous copies;
+    with more rows they go to the tcgen05 kernels; `streaming` asks for the register-fed
+    weight-streaming kernel (the one that also serves grouped products) whatever the row count.
     """
     if isinstance(x, NormedInput):
         nx = x
@@ -386,6 +388,11 @@ def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
         raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
     hint = rows_hint if rows_hint > 0 else M
     tc = _OPTIONAL_TC[0]
+    if not streaming and group_offsets is None and M <= SMALL_M:
+        # the decode step: W streamed through rings of asynchronous copies in shared memory
+        _check(L.leb_gemm_bf16_stream(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
+                                      epilogue, _stream()))
+        return
     # few dozen rows: W as the wide operand with K sliced over blocks, unless N alone already gives
     # every SM several tiles (the output head), where the persistent kernel streams W better
     if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296

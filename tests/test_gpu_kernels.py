@@ -113,6 +113,36 @@ def test_linear_bf16_small(M, N, K_):
     assert torch.equal(one.cpu()[0], out.cpu()[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K_", [(48, 72), (100, 200), (17, 40), (2048, 2048), (6144, 136), (352, 5632), (9600, 64)])
+def test_linear_bf16_stream(M, N, K_):
+    """The decode product (weights through rings of asynchronous copies): widths that leave part
+    of a tile, K that leaves part of a chunk or gives some warps nothing, more tiles than blocks."""
+    x, w = gen(M, K_, seed=9, dtype=torch.bfloat16), gen(N, K_, seed=10, scale=0.05, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV))
+    assert err(out, want) < 1e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=11).to(DEV)
+    b0 = base.clone()
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert err(base, b0.cpu().double() + want) < 1e-5
+    one = torch.empty(1, N, device=DEV)
+    K().linear(one, x[M - 1:].to(DEV), w.to(DEV))
+    assert torch.equal(one.cpu()[0], out.cpu()[M - 1])      # a row does not depend on the other rows
+    if N % 32 == 0:
+        from lastengine_b200.parts.ffn import fuse_gate_up
+        F = N // 2
+        w13 = fuse_gate_up(w[:F], w[F:], True).to(DEV)
+        sw = P.silu(want[:, :F]) * want[:, F:]
+        o2 = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+        K().linear(o2, x.to(DEV), w13, K().SWIGLU)
+        assert err(o2, sw) < 6e-3
+
+
 @pytest.mark.parametrize("M,F,D", [(3, 48, 72), (40, 160, 96), (70, 16, 40)])
 def test_linear_bf16_swiglu_epilogue(M, F, D):
     from lastengine_b200.parts.ffn import fuse_gate_up
