@@ -305,7 +305,11 @@ SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcg
 
 # Forming the norm inside the product saves a launch per product but puts the sum of squares in
 # front of every block's weight stream; measured on B200 (hidden 2048, batch 1 and 8) a decode
-# step got 10% slower, so it is off.  The path stays tested.
+# step got 10% slower, so it is off.  The path stays tested.  (The same was measured for the norm
+# formed in the tail of the product before it, by the block that finishes last, and for the norm
+# inside the ring-fed kernel: with programmatic dependent launch the small norm kernel between two
+# products is the window in which the next product starts up and prefetches its weights, so
+# taking it out saves nothing.)
 FUSE_NORM = False
 
 
