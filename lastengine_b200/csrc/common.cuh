@@ -47,11 +47,17 @@ static inline cudaError_t leb_launch(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.numAttrs = g_leb_pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
-// Device side: wait until the previous kernel on the stream has completed and its writes are
-// visible (a no-op for a plain launch), then let the next kernel start its own start-up.
+// Device side.  pdl_trigger(): the next kernel on the stream may be scheduled (once every block
+// of this one has said so); it then runs its own start-up and waits in its pdl_wait() until this
+// kernel has completed.  Said first thing, even before this kernel's own wait: a product two
+// launches down the stream can then fetch its weights while the one before it still runs (its
+// wait covers everything before it, since the kernel it waits for has itself waited).
+// pdl_wait(): wait until the previous kernel has completed and its writes are visible (a no-op
+// for a plain launch).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() {
+  pdl_trigger();
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 #define LEB_REQUIRE(cond, ...)                 \

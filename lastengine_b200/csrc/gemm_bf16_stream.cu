@@ -54,6 +54,7 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
                         int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles) {
   constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
   extern __shared__ __align__(128) unsigned char st_smem[];
+  pdl_trigger();
   float (*red)[NSUB][ST_ROWS][8 * MT + 1] =
       reinterpret_cast<float (*)[NSUB][ST_ROWS][8 * MT + 1]>(st_smem + (size_t)ST_WARPS * S * STAGE);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
