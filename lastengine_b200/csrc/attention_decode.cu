@@ -10,7 +10,10 @@
 // Both products run as mma.m16n8k16 with the G <= 16 query heads of the kv head as the 16 rows:
 //   S[head, pos]  = Q[head, :] . K[pos, :]         A = Q (registers), B = K rows from the cache
 //   O[head, dim] += P[head, pos] . V[pos, dim]     A = P (the S accumulators), B = V^T rows
-// Fragments come straight from global memory in 16-byte pieces, no shared-memory staging:
+// Every warp keeps a ring of stages in shared memory (keys [32][head_dim] and values
+// [head_dim][32] of one block of positions) filled by asynchronous copies, two or more blocks
+// ahead of the one it multiplies, so the memory latency is paid once per warp and not once per
+// block; fragments are read from a stage in 16-byte pieces laid out as in the cache:
 //  * over head_dim, a lane's 8 contiguous values feed two k16 steps as pairs (0,1)(2,3) and
 //    (4,5)(6,7); Q uses the same assignment, and a dot product does not care about the order;
 //  * the value cache is stored [dim][position] per page, so a lane's 16 bytes are 8 positions of
@@ -33,6 +36,17 @@ __device__ __forceinline__ void mma16816(float* d, uint32_t a0, uint32_t a1, uin
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+__device__ __forceinline__ void atd_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 atd_lds(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// stages of a warp's ring: 8 KB each at head size 64; two blocks per SM up to there
+#define ATD_STAGES(HD) ((HD) <= 64 ? 3 : 2)
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -62,8 +76,17 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
                         int n_splits) {
   constexpr int KB = HD / 32;  // 32-wide pieces of head_dim
   constexpr int NT = HD / 8;   // 8-wide output tiles over head_dim
-  __shared__ float o_s[ATD_WARPS][16][HD + 4];
-  __shared__ float m_s[ATD_WARPS][16], l_s[ATD_WARPS][16];
+  constexpr int S = ATD_STAGES(HD);
+  constexpr int KBYTES = 32 * HD * 2, STAGE = 2 * KBYTES;   // keys, then values
+  // head sizes whose key rows are a multiple of 128 bytes: the pieces of odd rows are moved by 4
+  // places so that the two rows a quarter-warp reads fall on different banks
+  constexpr int SWZ = (HD % 64 == 0) ? 4 : 0;
+  extern __shared__ __align__(128) unsigned char atd_smem[];
+  // after the loop the rings are done with and the same memory holds the warps' results
+  float (*o_s)[16][HD + 4] = reinterpret_cast<float (*)[16][HD + 4]>(atd_smem);
+  float (*m_s)[16] = reinterpret_cast<float (*)[16]>(atd_smem + sizeof(float) * ATD_WARPS * 16 * (HD + 4));
+  float (*l_s)[16] = m_s + ATD_WARPS;
+  static_assert(sizeof(float) * ATD_WARPS * 16 * (HD + 4 + 2) <= (size_t)ATD_WARPS * S * STAGE, "results must fit the rings");
 
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -119,41 +142,54 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     for (int e = 0; e < 4; e++) acc[n][e] = 0.f;
 
   const int* table = block_table + (size_t)b * bt_width;
-  uint4 kf[4][KB], vf[NT];      // the block being multiplied
-  uint4 kn[4][KB], vn[NT];      // this warp's next block, in flight meanwhile (small heads only)
-  constexpr bool PREFETCH = HD <= 64;
-  auto load_block = [&](int blk, uint4 (&kd)[4][KB], uint4 (&vd)[NT]) {
-    const int key0 = blk * 32;
-    const int page = table[key0 / page_size];
-    const int off = key0 % page_size;
-    const bf16* kbase = k_pool + (((size_t)page * nkv + kvh) * page_size + off) * HD;
-    const bf16* vbase = v_pool + ((size_t)page * nkv + kvh) * HD * page_size + off;
-    // keys: tile t, column n = r -> position 8*(r/2) + 2t + (r%2)
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(atd_smem) + warp * (S * STAGE);
+  int p_blk = blk_lo + warp, p_q = 0;      // the next block to ask for and its stage number
+  auto issue = [&]() {
+    if (p_blk < blk_hi) {
+      const int key0 = p_blk * 32;
+      const int page = table[key0 / page_size];
+      const int off = key0 % page_size;
+      const bf16* kbase = k_pool + (((size_t)page * nkv + kvh) * page_size + off) * HD;   // 32 rows of HD, contiguous
+      const bf16* vbase = v_pool + ((size_t)page * nkv + kvh) * HD * page_size + off;     // HD rows, 32 positions of each
+      const uint32_t base = ring + (p_q % S) * STAGE;
+      constexpr int KP = HD / 8;             // 16-byte pieces of a key row
 #pragma unroll
-    for (int t = 0; t < 4; t++) {
-      const int kp = 8 * (r >> 1) + 2 * t + (r & 1);
+      for (int i = 0; i < KP; i++) {         // 32 rows x KP pieces, 32 pieces a pass
+        const int idx = i * 32 + lane, row = idx / KP, pc = idx % KP;
+        atd_cp16(base + row * (HD * 2) + ((pc ^ ((row & 1) * SWZ)) << 4), kbase + (size_t)row * HD + pc * 8);
+      }
 #pragma unroll
-      for (int j = 0; j < KB; j++)
-        kd[t][j] = *reinterpret_cast<const uint4*>(kbase + (size_t)kp * HD + 32 * j + 8 * c);
+      for (int i = 0; i < HD / 8; i++) {     // HD rows x 4 pieces
+        const int idx = i * 32 + lane, row = idx >> 2, pc = idx & 3;
+        atd_cp16(base + KBYTES + row * 64 + (pc << 4), vbase + (size_t)row * page_size + pc * 8);
+      }
+      p_blk += ATD_WARPS;
+      p_q++;
     }
-    // values: output tile n, dimension 8n + r, positions 8c..8c+7 of the block
-#pragma unroll
-    for (int n = 0; n < NT; n++)
-      vd[n] = *reinterpret_cast<const uint4*>(vbase + (size_t)(8 * n + r) * page_size + 8 * c);
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (PREFETCH && blk_lo + warp < blk_hi) load_block(blk_lo + warp, kn, vn);
-  for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS) {
+#pragma unroll
+  for (int i = 0; i < S - 1; i++) issue();
+  uint4 kf[4][KB], vf[NT];      // the block being multiplied
+  int q_stage = 0;
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS, q_stage++) {
     const int key0 = blk * 32;
-    if (PREFETCH) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(S - 2) : "memory");
+    __syncwarp();     // every lane's pieces of this stage have landed; everyone is done with the stage before
+    issue();
+    {
+      const uint32_t base = ring + (q_stage % S) * STAGE;
+      // keys: tile t, column n = r -> position 8*(r/2) + 2t + (r%2)
 #pragma unroll
-      for (int t = 0; t < 4; t++)
+      for (int t = 0; t < 4; t++) {
+        const int kp = 8 * (r >> 1) + 2 * t + (r & 1);
 #pragma unroll
-        for (int j = 0; j < KB; j++) kf[t][j] = kn[t][j];
+        for (int j = 0; j < KB; j++)
+          kf[t][j] = atd_lds(base + kp * (HD * 2) + (((4 * j + c) ^ ((kp & 1) * SWZ)) << 4));
+      }
+      // values: output tile n, dimension 8n + r, positions 8c..8c+7 of the block
 #pragma unroll
-      for (int n = 0; n < NT; n++) vf[n] = vn[n];
-      if (blk + ATD_WARPS < blk_hi) load_block(blk + ATD_WARPS, kn, vn);
-    } else {
-      load_block(blk, kf, vf);
+      for (int n = 0; n < NT; n++) vf[n] = atd_lds(base + KBYTES + (8 * n + r) * 64 + (c << 4));
     }
     const bool partial = key0 < key_lo || key0 + 32 > kv_len;
     if (partial) {
@@ -222,6 +258,8 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     }
   }
 
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();    // the rings are no longer read or written: their memory takes the results
   // merge the warps: acc[n][0..1] -> head r, dims 8n + 2c, +1; acc[n][2..3] -> head r + 8
 #pragma unroll
   for (int n = 0; n < NT; n++) {
@@ -285,7 +323,16 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
   dim3 grid(nkv, B, n_splits);
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_decode: grid too large");
 #define LEB_ATD(HD_)                                                                              \
-  leb_launch(attention_decode_kernel<HD_>, grid, dim3(32 * ATD_WARPS), 0, st,                     \
+  {                                                                                               \
+    constexpr int smem = ATD_WARPS * ATD_STAGES(HD_) * 2 * 32 * HD_ * 2;                           \
+    static bool set = false;                                                                      \
+    if (!set) {                                                                                   \
+      if (cudaFuncSetAttribute(attention_decode_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) \
+        return leb_fail("leb_attention_decode: %d bytes of shared memory per block refused", smem); \
+      set = true;                                                                                 \
+    }                                                                                             \
+  }                                                                                               \
+  leb_launch(attention_decode_kernel<HD_>, grid, dim3(32 * ATD_WARPS), ATD_WARPS * ATD_STAGES(HD_) * 2 * 32 * HD_ * 2, st, \
       (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,    \
       bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
       window, scale, n_splits)
