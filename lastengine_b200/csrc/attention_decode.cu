@@ -45,8 +45,10 @@ __device__ __forceinline__ uint4 atd_lds(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-// stages of a warp's ring: 8 KB each at head size 64; two blocks per SM up to there
-#define ATD_STAGES(HD) ((HD) <= 64 ? 3 : 2)
+// stages of a warp's ring (8 KB each at head size 64).  Two are enough to keep a block in flight
+// while one is multiplied, and leave room for three blocks per SM: the loop is a chain of
+// dependent tensor-core and exponential steps, and more warps hide it better than deeper rings.
+#define ATD_STAGES(HD) ((HD) <= 32 ? 3 : 2)
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -134,6 +136,9 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     }
   }
 
+  // scores are kept times log2(e), so that the exponentials are single exp2 steps
+  const float scale2 = scale * 1.4426950408889634f;
+  const bool upper = G > 8;   // rows 8..15 of the tiles hold heads at all
   float mx[2] = {ATD_NEG, ATD_NEG}, l[2] = {0.f, 0.f};
   float acc[NT][4];
 #pragma unroll
@@ -216,7 +221,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
       for (int e = 0; e < 4; e++) {
         const int kp = key0 + 8 * c + 2 * t + (e & 1);
         const bool valid = kp >= key_lo && kp < kv_len;
-        s[t][e] = valid ? s[t][e] * scale : ATD_NEG;
+        s[t][e] = valid ? s[t][e] * scale2 : ATD_NEG;
         tmax[e >> 1] = fmaxf(tmax[e >> 1], s[t][e]);
       }
     float corr[2];
@@ -225,7 +230,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
       tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 1));
       tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 2));
       const float mn = fmaxf(mx[hh], tmax[hh]);
-      corr[hh] = expf(mx[hh] - mn);
+      corr[hh] = exp2f(mx[hh] - mn);
       mx[hh] = mn;
     }
     float psum[2] = {0.f, 0.f};
@@ -235,7 +240,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        p[e] = s[t][e] > 0.5f * ATD_NEG ? expf(s[t][e] - mx[e >> 1]) : 0.f;
+        p[e] = (e < 2 || upper) && s[t][e] > 0.5f * ATD_NEG ? exp2f(s[t][e] - mx[e >> 1]) : 0.f;
         psum[e >> 1] += p[e];
       }
       pa[t][0] = pack_bf16(p[0], p[1]);
@@ -283,7 +288,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     float L = 0.f, a = 0.f;
 #pragma unroll
     for (int w = 0; w < ATD_WARPS; w++) {
-      const float f = expf(m_s[w][hh] - M);
+      const float f = exp2f(m_s[w][hh] - M);
       L += l_s[w][hh] * f;
       a += o_s[w][hh][d] * f;
     }
@@ -294,7 +299,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
       out[(m_row * nh + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? a / L * g : 0.f);
     } else {
       float* pp = part + ((m_row * nh + h) * n_splits + split) * (size_t)(HD + 2);
-      if (d == 0) { pp[0] = M; pp[1] = L; }
+      if (d == 0) { pp[0] = M * 0.6931471805599453f; pp[1] = L; }   // the merge works with natural exponents
       pp[2 + d] = a;
     }
   }
