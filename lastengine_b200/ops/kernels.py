@@ -54,6 +54,8 @@ def _declare(L) -> None:
         "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
         "leb_attention_prefill_supported": [I, I, I, I],
+        "leb_attention_prefill_tc_supported": [I, I, I, I],
+        "leb_attention_prefill_tc": [P, P, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
         "leb_attention_prefill": [P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_gemm_bf16_skinny_slices": [I, I],
         "leb_gemm_bf16_skinny_supported": [P, P, I, I, I],
@@ -246,6 +248,9 @@ def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
     return best
 
 
+TC_ATTENTION_MIN_ROWS = 8   # longest row count of a sequence from which prompts go to the tcgen05 attention
+
+
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
               block_table: torch.Tensor, batch, nh: int, nkv: int, hd: int, page_size: int,
               window: int, scale: float, gate: torch.Tensor | None = None,
@@ -281,6 +286,15 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         if n_splits > 1:
             _check(L.leb_attention_merge(_ptr(out), _ptr(scratch), BF16, _ptr(gate), gate_stride, M, nh, hd,
                                          n_splits, _stream()))
+        return
+    if (out.dtype == torch.bfloat16 and n_splits == 1 and batch.max_qlen >= TC_ATTENTION_MIN_ROWS
+            and q.stride(0) % 8 == 0 and L.leb_attention_prefill_tc_supported(nh, nkv, hd, page_size)):
+        # prompts: tcgen05 tiles of 128 (position, head) rows, pages brought in by TMA
+        _check(L.leb_attention_prefill_tc(
+            _ptr(out), _ptr(q), q.stride(0), M, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
+            block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),
+            _ptr(batch.seq_qlen), _ptr(gate), gate_stride, batch.n_seqs, nh, nkv, hd, page_size, window, float(scale),
+            batch.max_qlen, _ptr(_status_word(out.device)), _stream()))
         return
     if (out.dtype == torch.bfloat16 and n_splits == 1
             and L.leb_attention_prefill_supported(nh, nkv, hd, page_size)):

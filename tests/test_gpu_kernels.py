@@ -362,7 +362,54 @@ def test_attention_far_key_and_window_edge(dtype):
             assert hit == sees, (splits, window)
 
 
-@pytest.mark.parametrize("dtype,nh,nkv,hd", [(torch.float32, 6, 2, 48), (torch.bfloat16, 6, 2, 64), (torch.bfloat16, 6, 2, 48)])
+@pytest.mark.parametrize("nh,nkv", [(4, 4), (4, 2), (8, 2), (8, 1)])
+@pytest.mark.parametrize("window", [0, 150])
+def test_attention_long_prompts_on_tcgen05(nh, nkv, window):
+    """Head size 64 with 1, 2, 4 and 8 query heads per kv head: the tcgen05 prompt kernel.  Two
+    sequences of several tiles and pages; the second continues at a position that is no multiple
+    of anything.  Keys grow along the sequence, so every row's maximum moves many times by more
+    than the factor the kernel tolerates before it rescales; one early key dominates a late query;
+    unused places of the cache hold NaN."""
+    hd, page, dtype = 64, 64, torch.bfloat16
+    lens_k, pos0, qn = [700, 333], [0, 203], [700, 130]
+    ks = [gen(n, nkv, hd, seed=160 + i) * torch.linspace(0.2, 3.0, n)[:, None, None] for i, n in enumerate(lens_k)]
+    vs = [gen(n, nkv, hd, seed=170 + i) for i, n in enumerate(lens_k)]
+    qs = [gen(n, nh, hd, seed=180 + i) for i, n in enumerate(qn)]
+    far = 5
+    ks[0][far] = 0
+    ks[0][far, :, 0] = 60.0
+    qs[0][650, :, :] = 0
+    qs[0][650, :, 0] = 8.0                       # score 480/8 = 60 against a few elsewhere
+    ks, vs, qs = [t.to(dtype) for t in ks], [t.to(dtype) for t in vs], [t.to(dtype) for t in qs]
+    n_pages = 20
+    order = np.random.default_rng(7).permutation(n_pages).astype(np.int32)
+    page_lists = [order[:11].tolist(), order[11:17].tolist()]
+    pools_k = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    pools_v = torch.full((n_pages, nkv, hd, page), float("nan"), dtype=dtype)
+    for i in range(2):
+        for t in range(lens_k[i]):
+            pools_k[page_lists[i][t // page], :, t % page] = ks[i][t]
+            pools_v[page_lists[i][t // page], :, :, t % page] = vs[i][t]
+    table = np.full((2, 11), -1, dtype=np.int32)
+    for i, pl in enumerate(page_lists):
+        table[i, :len(pl)] = pl
+    batch = builder().build([0, 1], [[0] * n for n in qn], pos0, [], {0: table})
+    M = sum(qn)
+    out = torch.full((M, nh * hd), float("nan"), device=DEV, dtype=dtype)
+    K().attention(out, torch.cat(qs).reshape(M, nh * hd).to(DEV), pools_k.to(DEV), pools_v.to(DEV), batch.tables[0],
+                  batch, nh, nkv, hd, page, window, 0.125)
+    K().check_device_status()
+    r0 = 0
+    for i, n in enumerate(qn):
+        want = plain_attention(qs[i].double(), ks[i].double(), vs[i].double(), torch.arange(pos0[i], pos0[i] + n), window, 0.125)
+        assert err(out[r0:r0 + n].view(n, nh, hd), want) < 8e-3, i
+        r0 += n
+    if window == 0:
+        assert err(out[650].view(nh, hd)[0], vs[0][far, 0].double()) < 1e-2     # the far key's value, alone
+
+
+@pytest.mark.parametrize("dtype,nh,nkv,hd", [(torch.float32, 6, 2, 48), (torch.bfloat16, 6, 2, 64), (torch.bfloat16, 6, 2, 48),
+                                             (torch.bfloat16, 8, 2, 64), (torch.bfloat16, 8, 1, 64)])
 def test_attention_batch_of_unequal_sequences(dtype, nh, nkv, hd):
     """Several sequences in one launch, each with its own pages, lengths and row counts; one is padding."""
     page = 64
