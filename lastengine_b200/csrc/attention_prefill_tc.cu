@@ -57,6 +57,11 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
       ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ float ex2(float x) {   // 2^x, one special-function step; 2^(very negative) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -84,8 +89,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = gridDim.x - 1 - blockIdx.x;   // the tiles with the longest key range first
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // blocks start in the order x, y, z: kv heads vary fastest, and the tiles with the longest key
+  // range come first, for all heads, so that the short ones fill the gaps at the end
+  const int tile = gridDim.y - 1 - blockIdx.y;
+  const int kvh = blockIdx.x, b = blockIdx.z;
   const int qlen = seq_qlen[b], row0 = tile * TP;
   if (row0 >= qlen) return;
   const int rows = min(TP, qlen - row0);
@@ -139,10 +146,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_expect_tx(&q_full, Q_BYTES);
       for (int g = 0; g < GS; g++)
         tma_load_2d(sq + g * (TP * HD * 2), &map_q, &q_full, (h0 + g) * HD, (int)m_base);
+      int next_page = table[jb0];
       for (int i = 0; i < nblk && ok; i++) {
         const int s = i % NS;
+        int page = next_page;
+        if (i + 1 < nblk) next_page = table[jb0 + i + 1];   // asked for before the wait below
         if (!mbar_wait(&kv_empty[s], ((i / NS) & 1) ^ 1, abort_flag)) { atomicExch(status, 11); ok = false; break; }
-        int page = table[jb0 + i];
         if (page < 0) page = 0;   // a page the window has left behind: every key of it is masked
         const int y = (page * nkv + kvh) * PAGE;
         mbar_expect_tx(&k_full[s], KV_BYTES);
@@ -200,22 +209,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tmem_ld_wait();
       // columns [c_lo, c_hi] of this page are keys this row may see
       const int c_lo = max(0, key_lo_row - key0), c_hi = row_valid ? min(PAGE - 1, qpos - key0) : -1;
-      float rmax = ATC_NEG;
+      float rm[4] = {ATC_NEG, ATC_NEG, ATC_NEG, ATC_NEG};   // four chains instead of one of 64 steps
       if (c_lo == 0 && c_hi == PAGE - 1) {
 #pragma unroll
         for (int c = 0; c < PAGE; c++) {
           const float sc = __uint_as_float(v[c]) * scale2;
           v[c] = __float_as_uint(sc);
-          rmax = fmaxf(rmax, sc);
+          rm[c & 3] = fmaxf(rm[c & 3], sc);
         }
       } else {
 #pragma unroll
         for (int c = 0; c < PAGE; c++) {
           const float sc = (c >= c_lo && c <= c_hi) ? __uint_as_float(v[c]) * scale2 : ATC_NEG;
           v[c] = __float_as_uint(sc);
-          rmax = fmaxf(rmax, sc);
+          rm[c & 3] = fmaxf(rm[c & 3], sc);
         }
       }
+      const float rmax = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
       const float m_new = fmaxf(m_used, rmax);
       bool move = false;
       if (l == 0.f) m_used = m_new;                 // nothing accumulated for this row yet: O's row is zero
@@ -224,7 +234,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // O holds pages < i; the product of page i waits for this warp's P, so O is still once page i-1 is in
         if (!mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) { atomicExch(status, 17); ok = false; break; }
         tc_fence_after();
-        const float f = move ? exp2f(m_used - m_new) : 1.f;
+        const float f = move ? ex2(m_used - m_new) : 1.f;
 #pragma unroll
         for (int hcol = 0; hcol < HD; hcol += 32) {
           uint32_t o[32];
@@ -240,17 +250,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const float m_ref = m_used > 0.5f * ATC_NEG ? m_used : 0.f;
       uint32_t pk[32];
-      float psum = 0.f;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < PAGE; c += 2) {
-        const float s0 = __uint_as_float(v[c]), s1 = __uint_as_float(v[c + 1]);
-        const float p0 = s0 > 0.5f * ATC_NEG ? exp2f(s0 - m_ref) : 0.f;
-        const float p1 = s1 > 0.5f * ATC_NEG ? exp2f(s1 - m_ref) : 0.f;
-        psum += p0 + p1;
+        // a masked score is -1e30: 2^(that - m_ref) is exactly zero
+        const float p0 = ex2(__uint_as_float(v[c]) - m_ref), p1 = ex2(__uint_as_float(v[c + 1]) - m_ref);
+        ps[(c >> 1) & 3] += p0 + p1;
         __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
       }
-      l += psum;
+      l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
       // P[bsel] was last read by the product of page i-2
       if (i >= 2 && !mbar_wait(&pv_done[bsel], ((i - 2) >> 1) & 1, abort_flag)) { atomicExch(status, 18); ok = false; break; }
       tc_fence_after();
@@ -333,7 +342,7 @@ LEB_API int leb_attention_prefill_tc(void* out, const void* q, int q_stride, int
   if (tensor_map(&mq, q, M, nh * hd, q_stride, TP)) return 1;
   if (tensor_map(&mk, k_pool, n_pages * nkv * page_size, hd, hd, page_size)) return 1;
   if (tensor_map(&mv, v_pool, n_pages * nkv * hd, page_size, page_size, hd)) return 1;
-  dim3 grid(ceil_div(max_qlen, TP), nkv, B);
+  dim3 grid(nkv, ceil_div(max_qlen, TP), B);
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_prefill_tc: grid too large");
   const size_t smem = 1024 + 128 * 64 * 2 + 2 * ATC_STAGES * 64 * 64 * 2;
 #define LEB_ATC(GS_)                                                                                              \
