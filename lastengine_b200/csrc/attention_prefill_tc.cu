@@ -87,19 +87,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
 
-  pdl_wait();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // blocks start in the order x, y, z: kv heads vary fastest, and the tiles with the longest key
   // range come first, for all heads, so that the short ones fill the gaps at the end
   const int tile = gridDim.y - 1 - blockIdx.y;
   const int kvh = blockIdx.x, b = blockIdx.z;
-  const int qlen = seq_qlen[b], row0 = tile * TP;
-  if (row0 >= qlen) return;
+  const int qlen = seq_qlen[b], row0 = tile * TP;   // step data: copied in long before the kernel before this one
+  if (row0 >= qlen) {
+    pdl_wait();   // a kernel counts as complete when its blocks are: none may finish before its predecessor has
+    return;
+  }
   const int rows = min(TP, qlen - row0);
   const int pos0 = seq_pos0[b];
   const size_t m_base = (size_t)seq_qstart[b] + row0;
   const int h0 = kvh * GS;
   if (seq_slot[b] < 0) {   // a padding sequence: its rows are zero
+    pdl_wait();
     for (int idx = threadIdx.x; idx < rows * GS * (HD / 8); idx += blockDim.x) {
       const int i = idx / (GS * (HD / 8)), rest = idx % (GS * (HD / 8));
       reinterpret_cast<uint4*>(out + ((m_base + i) * nh + h0) * HD)[rest] = make_uint4(0, 0, 0, 0);
@@ -134,6 +138,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();      // barriers and tensor memory are set up; now q and the cache must be complete
   const uint32_t tmem = tmem_slot;
   const uint32_t t_o = tmem, t_s0 = tmem + 64, t_p0 = tmem + 192;   // O | S0 S1 | P0 P1 (columns)
   // instruction descriptor: float accumulate, bfloat16 operands, both K-major, N = 64, M = 128
@@ -353,7 +358,7 @@ LEB_API int leb_attention_prefill_tc(void* out, const void* q, int q_stride, int
         return leb_fail("leb_attention_prefill_tc: %zu bytes of shared memory per block refused", smem);        \
       set = true;                                                                                                 \
     }                                                                                                             \
-    attention_prefill_tc_kernel<GS_><<<grid, ATC_THREADS, smem, st>>>(                                            \
+    leb_launch(attention_prefill_tc_kernel<GS_>, grid, dim3(ATC_THREADS), smem, st,                               \
         mq, mk, mv, (bf16*)out, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen, (const bf16*)gate, \
         gate_stride, nh, nkv, window, scale, status);                                                             \
   }

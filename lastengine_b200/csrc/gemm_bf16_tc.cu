@@ -41,6 +41,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   float* stage_out = (float*)(tmem_slot + 4);   // 4 warps x 32 rows x 36 floats for the epilogue
 
+  pdl_trigger();   // the next kernel may set itself up meanwhile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nk = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
@@ -68,6 +69,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  pdl_wait();      // barriers and tensor memory are set up; now the kernel before must be done
 
   if (warp == 0 || warp == 6) {
     if (lane == 0) {
@@ -249,7 +251,7 @@ static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int 
   }
   const long tiles = (long)ceil_div(N, BN) * ceil_div(M, TC_BM);
   dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));
-  kern<<<grid, TC_THREADS, smem, st>>>(ma, mw, (TC*)C, M, N, K, ldc, epilogue, status);
+  leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_tc");
   return 0;
 }

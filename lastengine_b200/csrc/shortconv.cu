@@ -22,6 +22,7 @@ __global__ void shortconv_rows_kernel(T* __restrict__ y, const T* __restrict__ b
                                       const int* __restrict__ row_seq,
                                       const int* __restrict__ seq_slot,
                                       const int* __restrict__ seq_qstart, int D, int Lc) {
+  pdl_wait();
   int m = blockIdx.x;
   int ch = blockIdx.y * blockDim.x + threadIdx.x;
   if (ch >= D) return;
@@ -57,6 +58,7 @@ __global__ void shortconv_rows_bf16x8_kernel(bf16* __restrict__ y, const bf16* _
                                              const float* __restrict__ state, const int* __restrict__ row_seq,
                                              const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                                              int D, int Lc) {
+  pdl_wait();
   const int m = blockIdx.x;
   const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (ch0 >= D) return;
@@ -128,6 +130,7 @@ __global__ void __launch_bounds__(128) shortconv_rows_bf16x8_chunk_kernel(
     bf16* __restrict__ y, const bf16* __restrict__ bcx, const float* __restrict__ w,
     const float* __restrict__ bias, const float* __restrict__ state, const int* __restrict__ row_seq,
     const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart, int M, int D) {
+  pdl_wait();
   const int m0 = blockIdx.x * CONV_CHUNK;
   const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (ch0 >= D) return;
@@ -203,6 +206,7 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
                                        const int* __restrict__ seq_slot,
                                        const int* __restrict__ seq_qstart,
                                        const int* __restrict__ seq_qlen, int D, int Lc) {
+  pdl_wait();
   int b = blockIdx.x;
   int ch = blockIdx.y * blockDim.x + threadIdx.x;
   if (ch >= D) return;
@@ -279,27 +283,25 @@ LEB_API int leb_shortconv(void* y, const void* bcx, int dtype, const float* w, c
   }
   dim3 g1(M, ceil_div(D, 128)), g2(B, ceil_div(D, 128));
   if (dtype == LEB_F32) {
-    shortconv_rows_kernel<float><<<g1, block, 0, st>>>((float*)y, (const float*)bcx, w, bias, state,
-                                                       row_seq, seq_slot, seq_qstart, D, Lc);
-    shortconv_state_kernel<float><<<g2, block, 0, st>>>((const float*)bcx, state, seq_slot,
-                                                        seq_qstart, seq_qlen, D, Lc);
+    leb_launch(shortconv_rows_kernel<float>, g1, block, 0, st, (float*)y, (const float*)bcx, w, bias, (const float*)state,
+               row_seq, seq_slot, seq_qstart, D, Lc);
+    leb_launch(shortconv_state_kernel<float>, g2, block, 0, st, (const float*)bcx, state, seq_slot, seq_qstart, seq_qlen, D, Lc);
   } else if (dtype == LEB_BF16) {
     const bool vec = D % 8 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)bcx % 16) == 0;
     const dim3 gc(ceil_div(M, CONV_CHUNK), ceil_div(D / 8, 128));
     if (vec && Lc == 3 && M >= 256)
-      shortconv_rows_bf16x8_chunk_kernel<3><<<gc, block, 0, st>>>(
-          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, M, D);
+      leb_launch(shortconv_rows_bf16x8_chunk_kernel<3>, gc, block, 0, st,
+          (bf16*)y, (const bf16*)bcx, w, bias, (const float*)state, row_seq, seq_slot, seq_qstart, M, D);
     else if (vec && Lc == 4 && M >= 256)
-      shortconv_rows_bf16x8_chunk_kernel<4><<<gc, block, 0, st>>>(
-          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, M, D);
+      leb_launch(shortconv_rows_bf16x8_chunk_kernel<4>, gc, block, 0, st,
+          (bf16*)y, (const bf16*)bcx, w, bias, (const float*)state, row_seq, seq_slot, seq_qstart, M, D);
     else if (vec)
-      shortconv_rows_bf16x8_kernel<<<dim3(M, ceil_div(D / 8, 128)), block, 0, st>>>(
-          (bf16*)y, (const bf16*)bcx, w, bias, state, row_seq, seq_slot, seq_qstart, D, Lc);
+      leb_launch(shortconv_rows_bf16x8_kernel, dim3(M, ceil_div(D / 8, 128)), block, 0, st,
+          (bf16*)y, (const bf16*)bcx, w, bias, (const float*)state, row_seq, seq_slot, seq_qstart, D, Lc);
     else
-      shortconv_rows_kernel<bf16><<<g1, block, 0, st>>>((bf16*)y, (const bf16*)bcx, w, bias, state,
-                                                        row_seq, seq_slot, seq_qstart, D, Lc);
-    shortconv_state_kernel<bf16><<<g2, block, 0, st>>>((const bf16*)bcx, state, seq_slot,
-                                                       seq_qstart, seq_qlen, D, Lc);
+      leb_launch(shortconv_rows_kernel<bf16>, g1, block, 0, st, (bf16*)y, (const bf16*)bcx, w, bias, (const float*)state,
+                 row_seq, seq_slot, seq_qstart, D, Lc);
+    leb_launch(shortconv_state_kernel<bf16>, g2, block, 0, st, (const bf16*)bcx, state, seq_slot, seq_qstart, seq_qlen, D, Lc);
   } else {
     return leb_fail("leb_shortconv: unknown dtype %d", dtype);
   }
