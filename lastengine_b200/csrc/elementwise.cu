@@ -180,11 +180,17 @@ LEB_API int leb_swiglu(void* a, int out_dtype, const void* gu, int in_dtype, int
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in,
                                    const int* __restrict__ rows, int div, int D) {
+  pdl_wait();
   int p = blockIdx.x;
   int src = rows[p] / div;
   const T* a = in + (size_t)src * D;
   T* o = out + (size_t)p * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = a[i];
+  if ((((uintptr_t)a | (uintptr_t)o) & 15) == 0 && (D * sizeof(T)) % 16 == 0) {
+    const int n = D * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(o)[i] = reinterpret_cast<const uint4*>(a)[i];
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = a[i];
+  }
 }
 
 LEB_API int leb_gather_rows(void* out, const void* in, int dtype, const int* rows, int div, int P,
@@ -192,9 +198,9 @@ LEB_API int leb_gather_rows(void* out, const void* in, int dtype, const int* row
   if (P <= 0) return 0;
   LEB_REQUIRE(div >= 1, "leb_gather_rows: div must be positive");
   if (dtype == LEB_F32)
-    gather_rows_kernel<float><<<P, 128, 0, st>>>((float*)out, (const float*)in, rows, div, D);
+    leb_launch(gather_rows_kernel<float>, dim3(P), dim3(128), 0, st, (float*)out, (const float*)in, rows, div, D);
   else if (dtype == LEB_BF16)
-    gather_rows_kernel<bf16><<<P, 128, 0, st>>>((bf16*)out, (const bf16*)in, rows, div, D);
+    leb_launch(gather_rows_kernel<bf16>, dim3(P), dim3(128), 0, st, (bf16*)out, (const bf16*)in, rows, div, D);
   else
     return leb_fail("leb_gather_rows: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_gather_rows");

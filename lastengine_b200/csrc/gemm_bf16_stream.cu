@@ -183,6 +183,194 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
   st_wait<0>();
 }
 
+// The same stream for products grouped by expert: rows [off[e], off[e+1]) of A and C belong to
+// expert e, whose weights are W + e * w_group_stride.  The offsets are made on the device by the
+// step itself, so the tiles (expert, block of 8*MT rows, 16*NSUB weight rows) are counted here: the
+// block builds the running count of tiles per expert in shared memory and takes the tiles
+// b, b + grid, ... of that list; experts without rows have no tiles and cost nothing.  Nothing
+// is fetched before the wait (the offsets come from the kernel before this one).
+#define ST_MAX_GROUPS 256
+
+template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
+__global__ void __launch_bounds__(32 * ST_WARPS, 2)
+gemm_bf16_stream_grouped_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W, int N,
+                                int K, int lda, int ldc, int epilogue, const int* __restrict__ group_offsets,
+                                int n_groups, size_t w_group_stride) {
+  constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
+  extern __shared__ __align__(128) unsigned char st_smem[];
+  __shared__ int cum[ST_MAX_GROUPS + 1], offs[ST_MAX_GROUPS + 1];
+  pdl_wait();
+  float (*red)[NSUB][ST_ROWS][8 * MT + 1] =
+      reinterpret_cast<float (*)[NSUB][ST_ROWS][8 * MT + 1]>(st_smem + (size_t)ST_WARPS * S * STAGE);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(st_smem) + warp * (S * STAGE);
+  const int n_tiles_n = (N + ROWS - 1) / ROWS;
+  for (int e = threadIdx.x; e <= n_groups; e += blockDim.x) offs[e] = group_offsets[e];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int c = 0;
+    for (int e = 0; e < n_groups; e++) {
+      cum[e] = c;
+      c += ((offs[e + 1] - offs[e] + 8 * MT - 1) / (8 * MT)) * n_tiles_n;
+    }
+    cum[n_groups] = c;
+  }
+  __syncthreads();
+  const int n_tiles = cum[n_groups];
+  const int n_chunks = (K + ST_CHUNK - 1) / ST_CHUNK;
+  const int my_chunks = warp < n_chunks ? (n_chunks - warp + ST_WARPS - 1) / ST_WARPS : 0;
+  const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int total = my_tiles * my_chunks;
+
+  struct Tile {
+    const bf16* w;   // the expert's weights
+    int n0, row0, rows;
+  };
+  auto tile_of = [&](int t) {
+    int lo = 0, hi = n_groups;   // the expert e with cum[e] <= t < cum[e + 1] (experts without tiles are passed over)
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (cum[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int local = t - cum[lo];
+    Tile r;
+    r.w = W + (size_t)lo * w_group_stride;
+    r.n0 = (local % n_tiles_n) * ROWS;
+    r.row0 = offs[lo] + (local / n_tiles_n) * (8 * MT);
+    r.rows = min(8 * MT, offs[lo + 1] - r.row0);
+    return r;
+  };
+
+  int p_q = 0, p_tile = blockIdx.x, p_ci = 0;
+  Tile pt = my_tiles > 0 ? tile_of(p_tile) : Tile{W, 0, 0, 0};
+  auto issue = [&]() {
+    if (p_q < total) {
+      const int k0 = (warp + ST_WARPS * p_ci) * ST_CHUNK;
+      const uint32_t base = ring + (p_q % S) * STAGE;
+#pragma unroll
+      for (int i = 0; i < 2 * MT; i++) {
+        const int row = i * 4 + (lane >> 3), ch = lane & 7;
+        const int k = k0 + ch * 8;
+        const bool in = row < pt.rows && k < K;
+        st_cp16(base + XOFF + row * 128 + ((ch ^ ((row & 1) << 2)) << 4), A + (in ? (size_t)(pt.row0 + row) * lda + k : 0), in ? 16 : 0);
+      }
+#pragma unroll
+      for (int i = 0; i < ROWS / 4; i++) {
+        const int row = i * 4 + (lane >> 3), ch = lane & 7;
+        const int n = min(pt.n0 + row, N - 1), k = k0 + ch * 8;
+        const bool in = k < K;
+        st_cp16(base + row * 128 + ((ch ^ ((row & 1) << 2)) << 4), pt.w + (size_t)n * K + (in ? k : 0), in ? 16 : 0);
+      }
+      p_q++;
+      if (++p_ci == my_chunks) {
+        p_ci = 0;
+        p_tile += gridDim.x;
+        if (p_tile < n_tiles) pt = tile_of(p_tile);
+      }
+    }
+    st_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < S - 1; i++) issue();
+  int q = 0;
+  for (int ti = 0; ti < my_tiles; ti++) {
+    const Tile ct = tile_of(blockIdx.x + ti * gridDim.x);
+    float acc[NSUB][MT][4];
+#pragma unroll
+    for (int s = 0; s < NSUB; s++)
+#pragma unroll
+      for (int t = 0; t < MT; t++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[s][t][e] = 0.f;
+    for (int ci = 0; ci < my_chunks; ci++, q++) {
+      st_wait<S - 2>();
+      __syncwarp();
+      issue();
+      const uint32_t base = ring + (q % S) * STAGE;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const uint32_t off = g * 128 + (((4 * j + t4) ^ ((g & 1) << 2)) << 4);
+        uint4 xc[MT];
+#pragma unroll
+        for (int t = 0; t < MT; t++) xc[t] = st_lds(base + XOFF + t * 8 * 128 + off);
+#pragma unroll
+        for (int s = 0; s < NSUB; s++) {
+          const uint4 w0 = st_lds(base + s * ST_ROWS * 128 + off), w1 = st_lds(base + s * ST_ROWS * 128 + off + 8 * 128);
+#pragma unroll
+          for (int t = 0; t < MT; t++) {
+            st_mma(acc[s][t], w0.x, w1.x, w0.y, w1.y, xc[t].x, xc[t].y);
+            st_mma(acc[s][t], w0.z, w1.z, w0.w, w1.w, xc[t].z, xc[t].w);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < NSUB; s++)
+#pragma unroll
+      for (int t = 0; t < MT; t++) {
+        red[warp][s][g][t * 8 + 2 * t4] = acc[s][t][0];
+        red[warp][s][g][t * 8 + 2 * t4 + 1] = acc[s][t][1];
+        red[warp][s][g + 8][t * 8 + 2 * t4] = acc[s][t][2];
+        red[warp][s][g + 8][t * 8 + 2 * t4 + 1] = acc[s][t][3];
+      }
+    __syncthreads();
+    if (epilogue == 2) {
+      const int jbase = ct.n0 / 2;   // gate rows 32j..32j+15 and up rows 32j+16..32j+31 give outputs 16j..16j+15
+      for (int idx = threadIdx.x; idx < ST_ROWS * 8 * MT; idx += blockDim.x) {
+        const int col = idx / ST_ROWS, i = idx % ST_ROWS;
+        if (col >= ct.rows || 2 * (jbase + i) >= N) continue;
+        float gt = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS; w++) {
+          gt += red[w][0][i][col];
+          up += red[w][NSUB - 1][i][col];
+        }
+        C[(size_t)(ct.row0 + col) * ldc + jbase + i] = from_f32<TC>(gt / (1.0f + expf(-gt)) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {
+        const int col = idx / ROWS, rr = idx % ROWS;
+        const int n = ct.n0 + rr;
+        if (col >= ct.rows || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS; w++) v += red[w][rr / ST_ROWS][rr % ST_ROWS][col];
+        TC* cp = C + (size_t)(ct.row0 + col) * ldc + n;
+        if (epilogue == 1) v += to_f32(*cp);
+        *cp = from_f32<TC>(v);
+      }
+    }
+    __syncthreads();
+  }
+  st_wait<0>();
+}
+
+template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
+static int launch_stream_grouped(void* C, const bf16* A, const bf16* W, int P, int N, int K, int lda, int ldc,
+                                 int epilogue, const int* group_offsets, int n_groups, size_t w_group_stride,
+                                 cudaStream_t st) {
+  constexpr int ROWS = ST_ROWS * NSUB;
+  constexpr size_t smem = (size_t)ST_WARPS * S * (ROWS + 8 * MT) * 128 + sizeof(float) * ST_WARPS * NSUB * ST_ROWS * (8 * MT + 1);
+  static int slots = 0;
+  if (!slots) {
+    int dev = 0, n_sm = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaFuncSetAttribute(gemm_bf16_stream_grouped_kernel<TC, MT, NSUB, S, ST_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return leb_fail("leb_gemm_bf16_stream_grouped: %zu bytes of shared memory per block refused", smem);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_bf16_stream_grouped_kernel<TC, MT, NSUB, S, ST_WARPS>, 32 * ST_WARPS, smem);
+    slots = max(1, per_sm) * max(1, n_sm);
+  }
+  // the most tiles the offsets can give: every expert may end with a partly filled block of rows
+  const long most = ((long)ceil_div(P, 8 * MT) + n_groups) * ceil_div(N, ROWS);
+  const int grid = (int)(most < slots ? most : slots);
+  leb_launch(gemm_bf16_stream_grouped_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st,
+             (TC*)C, A, W, N, K, lda, ldc, epilogue, group_offsets, n_groups, w_group_stride);
+  LEB_CHECK_LAUNCH("leb_gemm_bf16_stream_grouped");
+  return 0;
+}
+
 template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, int K, int lda, int ldc,
                          int epilogue, cudaStream_t st) {
@@ -234,4 +422,36 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
   if (c_dtype == LEB_BF16) return stream_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
   if (c_dtype == LEB_F32) return stream_dispatch<float>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
   return leb_fail("leb_gemm_bf16_stream: unknown C dtype %d", c_dtype);
+}
+
+template <typename TC>
+static int stream_grouped_dispatch(void* C, const bf16* a, const bf16* w, int P, int N, int K, int lda, int ldc,
+                                   int epilogue, const int* off, int n_groups, size_t stride, cudaStream_t st) {
+  const bool few = P <= 8 * n_groups;   // on average at most 8 rows per expert: blocks of 8 rows, else of 16
+  if (epilogue == 2) {
+    if (few) return launch_stream_grouped<TC, 1, 2, 4, 4>(C, a, w, P, N, K, lda, ldc, epilogue, off, n_groups, stride, st);
+    return launch_stream_grouped<TC, 2, 2, 4, 4>(C, a, w, P, N, K, lda, ldc, epilogue, off, n_groups, stride, st);
+  }
+  if (few) return launch_stream_grouped<TC, 1, 1, 4, 8>(C, a, w, P, N, K, lda, ldc, epilogue, off, n_groups, stride, st);
+  return launch_stream_grouped<TC, 2, 1, 3, 8>(C, a, w, P, N, K, lda, ldc, epilogue, off, n_groups, stride, st);
+}
+
+// Grouped form: rows [group_offsets[e], group_offsets[e+1]) of A [P, K] and C go with the weights
+// W + e * w_group_stride ([N, K] each).  group_offsets [n_groups + 1] lives on the device.
+LEB_API int leb_gemm_bf16_stream_grouped(void* C, int c_dtype, const void* A, const void* W, int P, int N, int K,
+                                         int lda, int ldc, int epilogue, const int* group_offsets, int n_groups,
+                                         size_t w_group_stride, cudaStream_t st) {
+  if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
+  LEB_REQUIRE(n_groups <= ST_MAX_GROUPS, "leb_gemm_bf16_stream_grouped: %d groups; at most %d", n_groups, ST_MAX_GROUPS);
+  LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "leb_gemm_bf16_stream_grouped: K (%d) and the row stride of A (%d) must be multiples of 8", K, lda);
+  LEB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (w_group_stride * 2) % 16 == 0,
+              "leb_gemm_bf16_stream_grouped: A, W and the distance between experts must be 16-byte aligned");
+  LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_stream_grouped: unknown epilogue %d", epilogue);
+  LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_stream_grouped: adding needs a float C");
+  LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_stream_grouped: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
+  if (c_dtype == LEB_BF16)
+    return stream_grouped_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, P, N, K, lda, ldc, epilogue, group_offsets, n_groups, w_group_stride, st);
+  if (c_dtype == LEB_F32)
+    return stream_grouped_dispatch<float>(C, (const bf16*)A, (const bf16*)W, P, N, K, lda, ldc, epilogue, group_offsets, n_groups, w_group_stride, st);
+  return leb_fail("leb_gemm_bf16_stream_grouped: unknown C dtype %d", c_dtype);
 }

@@ -23,10 +23,19 @@
 // *status, every role leaves its loop, tensor memory is freed, and the block returns.
 #include "tc_common.cuh"
 
-template <typename TC, int BN, int STAGES>
+#define TC_MAX_GROUPS 256
+
+// GROUPED: rows [off[e], off[e+1]) of A and C go with expert e's weights, rows [e*N, (e+1)*N) of the
+// stacked W.  The offsets are made on the device by the step itself, so the tiles (expert, 128
+// rows of it, BN weight rows) are counted in the kernel: a running count of tiles per expert in
+// shared memory, and every role walks the tiles b, b + grid, ... of that list.  A tile's last
+// rows may belong to the next expert: they are computed and not stored.
+template <typename TC, int BN, int STAGES, bool GROUPED>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    TC* __restrict__ C, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status) {
+                    TC* __restrict__ C, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status,
+                    const int* __restrict__ group_offsets, int n_groups) {
+  __shared__ int g_cum[GROUPED ? TC_MAX_GROUPS + 1 : 1], g_off[GROUPED ? TC_MAX_GROUPS + 1 : 1];
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -45,7 +54,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nk = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;   // tile t: rows (t % m_tiles), columns (t / m_tiles):
+  int num_tiles = m_tiles * n_tiles;         // tile t: rows (t % m_tiles), columns (t / m_tiles):
                                              // blocks running together share weight tiles in L2
 
   if (threadIdx.x == 0) {
@@ -70,6 +79,44 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
   pdl_wait();      // barriers and tensor memory are set up; now the kernel before must be done
+  if (GROUPED) {
+    for (int e = threadIdx.x; e <= n_groups; e += blockDim.x) g_off[e] = group_offsets[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int c = 0;
+      for (int e = 0; e < n_groups; e++) {
+        g_cum[e] = c;
+        c += ((g_off[e + 1] - g_off[e] + TC_BM - 1) / TC_BM) * n_tiles;
+      }
+      g_cum[n_groups] = c;
+    }
+    __syncthreads();
+    num_tiles = g_cum[n_groups];
+  }
+  // where a tile lies: first row of A and C, the row its rows end at, first column of C, first
+  // row of W, and the index of its column tile
+  auto place = [&](int tile, int& m0, int& m_end, int& n0, int& w0, int& nt) {
+    if (GROUPED) {
+      int lo = 0, hi = n_groups;   // the expert with g_cum[lo] <= tile < g_cum[lo + 1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (g_cum[mid] <= tile) lo = mid; else hi = mid;
+      }
+      const int local = tile - g_cum[lo];
+      const int mt = (g_off[lo + 1] - g_off[lo] + TC_BM - 1) / TC_BM;
+      nt = local / mt;
+      m0 = g_off[lo] + (local % mt) * TC_BM;
+      m_end = g_off[lo + 1];
+      n0 = nt * BN;
+      w0 = lo * N + n0;
+    } else {
+      nt = tile / m_tiles;
+      m0 = (tile % m_tiles) * TC_BM;
+      m_end = M;
+      n0 = nt * BN;
+      w0 = n0;
+    }
+  };
 
   if (warp == 0 || warp == 6) {
     if (lane == 0) {
@@ -77,16 +124,17 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0;   // k-slices loaded so far, over all tiles of this block
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+        int m0, m_end, n0, w0, nt;
+        place(tile, m0, m_end, n0, w0, nt);
         for (int kb = 0; kb < nk; kb++, it++) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 1); ok = false; break; }
           mbar_expect_tx(&full[s], loads_a ? A_BYTES : B_BYTES);
           // Tiles that share rows of A start their walk over k at different places, so that
           // blocks running in step do not all ask L2 for the same lines at the same moment.
-          const int kk = (kb + (tile / m_tiles) * 5) % nk;
+          const int kk = (kb + nt * 5) % nk;
           if (loads_a) tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kk * TC_BK, m0);
-          else tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kk * TC_BK, n0);
+          else tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kk * TC_BK, w0);
         }
       }
     }
@@ -125,7 +173,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     float* stg = stage_out + quad * (32 * 36);
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, t++) {
-    const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+    int m0, m_end, n0, w0, nt;
+    place(tile, m0, m_end, n0, w0, nt);
     const uint32_t buf = t & 1;
     const int row_base = m0 + quad * 32;
     bool ok = mbar_wait(&acc_full[buf], (t >> 1) & 1, abort_flag);
@@ -173,13 +222,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const int row = row_base + lr + 4 * it;
-            old[it] = row < M ? __ldcs(reinterpret_cast<const float4*>(C + (size_t)row * ldc + col))
+            old[it] = row < m_end ? __ldcs(reinterpret_cast<const float4*>(C + (size_t)row * ldc + col))
                               : make_float4(0.f, 0.f, 0.f, 0.f);
           }
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const int rr = lr + 4 * it, row = row_base + rr;
-            if (row >= M) continue;
+            if (row >= m_end) continue;
             const float4 f = *reinterpret_cast<const float4*>(stg + rr * 36 + lc);
             *reinterpret_cast<float4*>(C + (size_t)row * ldc + col) =
                 make_float4(f.x + old[it].x, f.y + old[it].y, f.z + old[it].z, f.w + old[it].w);
@@ -189,7 +238,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int rr = lr; rr < 32; rr += rpp) {
           const int row = row_base + rr;
-          if (row >= M || col >= n_out) continue;
+          if (row >= m_end || col >= n_out) continue;
           float4 f = *reinterpret_cast<const float4*>(stg + rr * 36 + lc);
           TC* o = C + (size_t)row * ldc + col;
           if (vec && col + 3 < n_out) {
@@ -231,12 +280,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-template <typename TC, int BN, int STAGES>
+template <typename TC, int BN, int STAGES, bool GROUPED = false>
 static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int M, int N, int K, int ldc,
-                     int epilogue, int* status, cudaStream_t st) {
+                     int epilogue, int* status, cudaStream_t st, const int* group_offsets = nullptr, int n_groups = 0) {
   constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 +
                           4 * 32 * 36 * 4 + 1024;
-  auto kern = gemm_bf16_tc_kernel<TC, BN, STAGES>;
+  auto kern = gemm_bf16_tc_kernel<TC, BN, STAGES, GROUPED>;
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -249,9 +298,11 @@ static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int 
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
   }
-  const long tiles = (long)ceil_div(N, BN) * ceil_div(M, TC_BM);
+  // grouped: the most tiles the offsets can give (every expert may end with a partly filled tile)
+  const long tiles = (long)ceil_div(N, BN) * (ceil_div(M, TC_BM) + (GROUPED ? n_groups : 0));
   dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));
-  leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status);
+  leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status, group_offsets,
+             n_groups);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_tc");
   return 0;
 }
@@ -295,4 +346,32 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
     return launch_tc<float, 32, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   return leb_fail("leb_gemm_bf16_tc: unknown C dtype %d", c_dtype);
+}
+
+// Grouped form for experts with many rows each (prompts): A [P, K] and C sorted by expert, rows
+// [group_offsets[e], group_offsets[e+1]) with the weights W[e] ([n_groups, N, K] stacked);
+// group_offsets [n_groups + 1] lives on the device.
+LEB_API int leb_gemm_bf16_tc_grouped(void* C, int c_dtype, const void* A, const void* W, int P, int N, int K, int lda,
+                                     int ldc, int epilogue, const int* group_offsets, int n_groups, int* status,
+                                     cudaStream_t st) {
+  if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
+  LEB_REQUIRE(n_groups <= TC_MAX_GROUPS, "leb_gemm_bf16_tc_grouped: %d groups; at most %d", n_groups, TC_MAX_GROUPS);
+  LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc_grouped: operands not aligned for TMA (K %d, lda %d)", K, lda);
+  LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_tc_grouped: unknown epilogue %d", epilogue);
+  LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_tc_grouped: adding needs a float C");
+  LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_tc_grouped: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
+  LEB_REQUIRE(status != nullptr && group_offsets != nullptr, "leb_gemm_bf16_tc_grouped: a status word and the offsets are required");
+  LEB_REQUIRE((long)n_groups * N < (1L << 31), "leb_gemm_bf16_tc_grouped: %d x %d weight rows do not fit a tensor map coordinate", n_groups, N);
+  CUtensorMap ma, mw;
+  if (tensor_map(&ma, A, P, K, lda, TC_BM)) return 1;
+  if (N > 128) {
+    if (tensor_map(&mw, W, n_groups * N, K, K, 256)) return 1;
+    if (c_dtype == LEB_BF16) return launch_tc<bf16, 256, 4, true>(C, ma, mw, P, N, K, ldc, epilogue, status, st, group_offsets, n_groups);
+    if (c_dtype == LEB_F32) return launch_tc<float, 256, 4, true>(C, ma, mw, P, N, K, ldc, epilogue, status, st, group_offsets, n_groups);
+  } else {
+    if (tensor_map(&mw, W, n_groups * N, K, K, 64)) return 1;
+    if (c_dtype == LEB_BF16) return launch_tc<bf16, 64, 8, true>(C, ma, mw, P, N, K, ldc, epilogue, status, st, group_offsets, n_groups);
+    if (c_dtype == LEB_F32) return launch_tc<float, 64, 8, true>(C, ma, mw, P, N, K, ldc, epilogue, status, st, group_offsets, n_groups);
+  }
+  return leb_fail("leb_gemm_bf16_tc_grouped: unknown C dtype %d", c_dtype);
 }

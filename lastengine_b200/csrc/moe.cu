@@ -12,51 +12,97 @@
 #define MOE_MAX_E 256
 #define MOE_MAX_K 16
 
-template <typename T>
-__global__ void moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w,
-                                  const T* __restrict__ h, const float* __restrict__ wr,
-                                  const float* __restrict__ bias, int D, int E, int k, int norm_topk,
-                                  float scaling) {
-  extern __shared__ float sm[];  // h row as float [D], then s[E], c[E]
+// A block takes R rows; warp w takes experts w, w + warps, ...: it reads the expert's router row
+// once (16-byte loads when D is a multiple of 4) and forms the dot product with each of the R
+// rows, so a single row costs one pass of one warp per expert, all experts at once, and many rows
+// share the router's weights R at a time.  A lane's partial sum runs over elements lane, lane +
+// 32, ... (in pieces of VEC), whatever R and the number of rows are: a row's scores do not
+// depend on the rows around it.  The top k are then found by warp 0 with shuffles.
+template <typename T, int R, int VEC>
+__global__ void __launch_bounds__(1024)
+moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const T* __restrict__ h,
+                  const float* __restrict__ wr, const float* __restrict__ bias, int M, int D, int E, int k,
+                  int norm_topk, float scaling) {
+  extern __shared__ __align__(16) float sm[];  // R rows of h as float [R][D], then s[R][E], c[R][E]
   float* hs = sm;
-  float* s_ = hs + D;
-  float* c_ = s_ + E;
-  const int m = blockIdx.x;
+  float* s_ = hs + (size_t)R * D;
+  float* c_ = s_ + R * E;
+  pdl_wait();
+  const int m0 = blockIdx.x * R;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) hs[i] = to_f32(h[(size_t)m * D + i]);
+  for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+    const int r = i / D;
+    hs[i] = m0 + r < M ? to_f32(h[(size_t)(m0 + r) * D + (i - r * D)]) : 0.f;
+  }
   __syncthreads();
   for (int e = warp; e < E; e += nw) {
     const float* w = wr + (size_t)e * D;
-    float z = 0.f;
-    for (int i = lane; i < D; i += 32) z += w[i] * hs[i];
-    z = warp_sum(z);
-    if (lane == 0) {
-      float s = 1.0f / (1.0f + expf(-z));
-      s_[e] = s;
-      c_[e] = s + (bias ? bias[e] : 0.f);
+    float z[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) z[r] = 0.f;
+    if (VEC == 4) {
+      const float4* w4 = reinterpret_cast<const float4*>(w);
+      for (int i = lane; i < D / 4; i += 32) {
+        const float4 a = w4[i];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const float4 x = reinterpret_cast<const float4*>(hs + (size_t)r * D)[i];
+          z[r] += a.x * x.x;
+          z[r] += a.y * x.y;
+          z[r] += a.z * x.z;
+          z[r] += a.w * x.w;
+        }
+      }
+    } else {
+      for (int i = lane; i < D; i += 32) {
+        const float a = w[i];
+#pragma unroll
+        for (int r = 0; r < R; r++) z[r] += a * hs[(size_t)r * D + i];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const float zz = warp_sum(z[r]);
+      if (lane == 0) {
+        const float sg = 1.0f / (1.0f + expf(-zz));
+        s_[r * E + e] = sg;
+        c_[r * E + e] = sg + (bias ? bias[e] : 0.f);
+      }
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int ids[MOE_MAX_K];
+  // the k largest c of each row, ties to the lower index: warp r' takes rows r', r' + warps, ...
+  for (int r = warp; r < R; r += nw) {
+    if (m0 + r >= M) continue;
+    const float* c = c_ + r * E;
+    const float* sg = s_ + r * E;
+    unsigned taken = 0;   // bit j: this lane's candidate lane + 32 j is chosen already
+    int chosen[MOE_MAX_K];
     float sum = 0.f;
     for (int j = 0; j < k; j++) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < E; e++) {
-        bool taken = false;
-        for (int t = 0; t < j; t++) taken |= ids[t] == e;
-        if (taken) continue;
-        if (best < 0 || c_[e] > bv) { best = e; bv = c_[e]; }  // strict: ties keep the lower index
+      float bv = -INFINITY;
+      int be = 0x7fffffff;
+      for (int q = 0; lane + 32 * q < E; q++) {
+        const int e = lane + 32 * q;
+        if (!((taken >> q) & 1u) && (c[e] > bv || be == 0x7fffffff)) { bv = c[e]; be = e; }   // ascending e: ties keep the lower
       }
-      ids[j] = best;
-      sum += s_[best];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; }
+      }
+      if ((be & 31) == lane) taken |= 1u << (be >> 5);
+      chosen[j] = be;
+      sum += sg[be];
     }
-    for (int j = 0; j < k; j++) {
-      float w = s_[ids[j]];
-      if (norm_topk) w = w / sum;
-      topk_ids[(size_t)m * k + j] = ids[j];
-      topk_w[(size_t)m * k + j] = w * scaling;
+    if (lane == 0) {
+      for (int j = 0; j < k; j++) {
+        float w = sg[chosen[j]];
+        if (norm_topk) w = w / sum;
+        topk_ids[(size_t)(m0 + r) * k + j] = chosen[j];
+        topk_w[(size_t)(m0 + r) * k + j] = w * scaling;
+      }
     }
   }
 }
@@ -67,14 +113,25 @@ LEB_API int leb_moe_router(int* topk_ids, float* topk_w, const void* h, int dtyp
   if (M <= 0) return 0;
   LEB_REQUIRE(E >= 1 && E <= MOE_MAX_E, "leb_moe_router: %d experts outside 1..%d", E, MOE_MAX_E);
   LEB_REQUIRE(k >= 1 && k <= MOE_MAX_K && k <= E, "leb_moe_router: top-%d outside 1..min(%d, experts)", k, MOE_MAX_K);
-  size_t smem = ((size_t)D + 2 * E) * sizeof(float);
+  // rows per block: 4 when there are many rows and they fit shared memory, else 1
+  const bool four = M >= 8 && ((size_t)4 * D + 8 * E) * sizeof(float) <= 48 * 1024;
+  const int R = four ? 4 : 1;
+  const size_t smem = ((size_t)R * D + 2 * R * E) * sizeof(float);
   LEB_REQUIRE(smem <= 48 * 1024, "leb_moe_router: hidden size %d too large for the router kernel", D);
-  if (dtype == LEB_F32)
-    moe_router_kernel<float><<<M, 128, smem, st>>>(topk_ids, topk_w, (const float*)h, wr, bias, D, E, k, norm_topk, scaling);
-  else if (dtype == LEB_BF16)
-    moe_router_kernel<bf16><<<M, 128, smem, st>>>(topk_ids, topk_w, (const bf16*)h, wr, bias, D, E, k, norm_topk, scaling);
-  else
+  const bool vec = D % 4 == 0 && ((uintptr_t)wr & 15) == 0;
+  const dim3 grid(ceil_div(M, R)), block(32 * (E < 32 ? E : 32));
+#define LEB_ROUTER(T_, R_, V_) \
+  leb_launch(moe_router_kernel<T_, R_, V_>, grid, block, smem, st, topk_ids, topk_w, (const T_*)h, wr, bias, M, D, E, k, norm_topk, scaling)
+  if (dtype == LEB_F32) {
+    if (four) { if (vec) LEB_ROUTER(float, 4, 4); else LEB_ROUTER(float, 4, 1); }
+    else { if (vec) LEB_ROUTER(float, 1, 4); else LEB_ROUTER(float, 1, 1); }
+  } else if (dtype == LEB_BF16) {
+    if (four) { if (vec) LEB_ROUTER(bf16, 4, 4); else LEB_ROUTER(bf16, 4, 1); }
+    else { if (vec) LEB_ROUTER(bf16, 1, 4); else LEB_ROUTER(bf16, 1, 1); }
+  } else {
     return leb_fail("leb_moe_router: unknown dtype %d", dtype);
+  }
+#undef LEB_ROUTER
   LEB_CHECK_LAUNCH("leb_moe_router");
   return 0;
 }
@@ -88,6 +145,7 @@ __global__ void moe_align_kernel(int* __restrict__ offsets, int* __restrict__ so
                                  int* __restrict__ pair_row, const int* __restrict__ topk_ids,
                                  int P, int E) {
   __shared__ int counts[MOE_MAX_E + 1];
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int e = warp; e < E; e += nw) {
     int cnt = 0;
@@ -131,7 +189,7 @@ LEB_API int leb_moe_align(int* offsets, int* sorted_pair, int* pair_row, const i
                           int E, cudaStream_t st) {
   LEB_REQUIRE(E >= 1 && E <= MOE_MAX_E, "leb_moe_align: %d experts outside 1..%d", E, MOE_MAX_E);
   if (P < 0) return leb_fail("leb_moe_align: negative pair count");
-  moe_align_kernel<<<1, 1024, 0, st>>>(offsets, sorted_pair, pair_row, topk_ids, P, E);
+  leb_launch(moe_align_kernel, dim3(1), dim3(1024), 0, st, offsets, sorted_pair, pair_row, topk_ids, P, E);
   LEB_CHECK_LAUNCH("leb_moe_align");
   return 0;
 }
@@ -140,6 +198,7 @@ LEB_API int leb_moe_align(int* offsets, int* sorted_pair, int* pair_row, const i
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys,
                                    const int* __restrict__ pair_row, const float* __restrict__ topk_w,
                                    int D, int k, int accumulate) {
+  pdl_wait();
   const size_t m = blockIdx.x;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float a = 0.f;
@@ -153,7 +212,7 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
 LEB_API int leb_moe_combine(float* x, const float* ys, const int* pair_row, const float* topk_w,
                             int M, int D, int k, int accumulate, cudaStream_t st) {
   if (M <= 0) return 0;
-  moe_combine_kernel<<<M, 256, 0, st>>>(x, ys, pair_row, topk_w, D, k, accumulate);
+  leb_launch(moe_combine_kernel, dim3(M), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
   LEB_CHECK_LAUNCH("leb_moe_combine");
   return 0;
 }

@@ -41,6 +41,8 @@ def _declare(L) -> None:
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
+        "leb_gemm_bf16_stream_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
+        "leb_gemm_bf16_tc_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gemm_bf16_small_norm": [P, I, P, I, P, F, P, I, I, I, I, I, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
         "leb_moe_align": [P, P, P, P, I, I, P],
@@ -417,6 +419,17 @@ def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
             and linear_skinny(out, x, w, epilogue)):
         return
     if tc is not None and not streaming and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
+        return
+    if (not streaming and group_offsets is not None and E <= 256 and M > 16 * E and w.is_contiguous()
+            and L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, lda)):
+        # experts with many rows each (prompts): tcgen05 tiles over the experts' row ranges
+        _check(L.leb_gemm_bf16_tc_grouped(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
+                                          epilogue, _ptr(group_offsets), E, _ptr(_status_word(x.device)), _stream()))
+        return
+    if not streaming and group_offsets is not None and E <= 256 and M <= 16 * E:
+        # experts with a few rows each (decode steps): the ring-fed stream over the experts that have rows
+        _check(L.leb_gemm_bf16_stream_grouped(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
+                                              epilogue, _ptr(group_offsets), E, stride, _stream()))
         return
     _check(L.leb_gemm_bf16_small(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
                                  epilogue, _ptr(group_offsets), E, stride, hint, _stream()))

@@ -171,6 +171,81 @@ def test_linear_grouped(dtype):
     assert err(out, want) < 1e-5
 
 
+@pytest.mark.parametrize("counts,N,K_", [([3, 0, 0, 1, 9, 0, 2], 48, 72), ([1, 0, 0, 0, 0, 0, 0, 4], 3584, 2048),
+                                         ([17, 8, 0, 33, 1, 16, 9, 5], 96, 200), ([5] * 32, 352, 136),
+                                         ([0, 0, 0, 0, 0, 0, 0, 0, 0, 7], 64, 64)])
+def test_linear_grouped_stream(counts, N, K_):
+    """Grouped products through the ring-fed kernel: experts without rows, with one row, with more
+    rows than one block of 8 or 16 takes; store, add, both result types, and the SwiGLU epilogue."""
+    E = len(counts)
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
+    Ptot = int(offs[-1])
+    assert Ptot <= 16 * E                                   # the sizes this kernel is chosen for
+    x, w = gen(Ptot, K_, seed=15, dtype=torch.bfloat16), gen(E, N, K_, seed=16, scale=0.05, dtype=torch.bfloat16)
+    want = torch.zeros(Ptot, N, dtype=torch.float64)
+    for e in range(E):
+        a, b = int(offs[e]), int(offs[e + 1])
+        want[a:b] = x[a:b].double() @ w[e].double().T
+    out = torch.full((Ptot, N), float("nan"), device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV), rows_hint=Ptot)
+    assert err(out, want) < 1e-5
+    old = torch.empty(Ptot, N, device=DEV)
+    K().linear(old, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV), rows_hint=Ptot, streaming=True)
+    assert err(old, want) < 1e-5                            # the register-fed kernel on the same groups
+    ob = torch.empty(Ptot, N, device=DEV, dtype=torch.bfloat16)
+    K().linear(ob, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(Ptot, N, seed=17).to(DEV)
+    b0 = base.clone()
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE, group_offsets=offs.to(DEV))
+    assert err(base, b0.cpu().double() + want) < 1e-5
+    if N % 32 == 0:
+        from lastengine_b200.parts.ffn import fuse_gate_up
+        F = N // 2
+        w13 = torch.stack([fuse_gate_up(w[e, :F], w[e, F:], True) for e in range(E)]).to(DEV)
+        sw = P.silu(want[:, :F]) * want[:, F:]
+        o2 = torch.empty(Ptot, F, device=DEV, dtype=torch.bfloat16)
+        K().linear(o2, x.to(DEV), w13, K().SWIGLU, group_offsets=offs.to(DEV))
+        assert err(o2, sw) < 6e-3
+
+
+@pytest.mark.parametrize("counts,N,K_", [([300, 0, 129, 1, 700, 128], 96, 200), ([5, 260, 0, 0, 131], 352, 136),
+                                         ([128, 128, 128], 512, 64), ([0, 0, 1000, 0], 3584, 256)])
+def test_linear_grouped_tcgen05(counts, N, K_):
+    """Grouped products with many rows per expert (prompts) on tcgen05: experts without rows, with
+    one row, with rows that end inside a tile (the tile's other rows belong to the next expert and
+    must not be written by this one), widths that end inside a weight tile."""
+    E = len(counts)
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
+    Ptot = int(offs[-1])
+    assert Ptot > 16 * E
+    x, w = gen(Ptot, K_, seed=15, dtype=torch.bfloat16), gen(E, N, K_, seed=16, scale=0.05, dtype=torch.bfloat16)
+    want = torch.zeros(Ptot, N, dtype=torch.float64)
+    for e in range(E):
+        a, b = int(offs[e]), int(offs[e + 1])
+        want[a:b] = x[a:b].double() @ w[e].double().T
+    out = torch.full((Ptot, N), float("nan"), device=DEV)
+    K().linear(out, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV), rows_hint=Ptot)
+    K().check_device_status()
+    assert err(out, want) < 2e-5
+    ob = torch.empty(Ptot, N, device=DEV, dtype=torch.bfloat16)
+    K().linear(ob, x.to(DEV), w.to(DEV), group_offsets=offs.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(Ptot, N, seed=17).to(DEV)
+    b0 = base.clone()
+    K().linear(base, x.to(DEV), w.to(DEV), K().ACCUMULATE, group_offsets=offs.to(DEV))
+    assert err(base, b0.cpu().double() + want) < 2e-5
+    if N % 32 == 0:
+        from lastengine_b200.parts.ffn import fuse_gate_up
+        F = N // 2
+        w13 = torch.stack([fuse_gate_up(w[e, :F], w[e, F:], True) for e in range(E)]).to(DEV)
+        sw = P.silu(want[:, :F]) * want[:, F:]
+        o2 = torch.empty(Ptot, F, device=DEV, dtype=torch.bfloat16)
+        K().linear(o2, x.to(DEV), w13, K().SWIGLU, group_offsets=offs.to(DEV))
+        assert err(o2, sw) < 6e-3
+    K().check_device_status()
+
+
 # ---- short convolution ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("Lc,D", [(3, 72), (4, 130), (2, 64)])
