@@ -113,8 +113,9 @@ LEB_API int leb_moe_router(int* topk_ids, float* topk_w, const void* h, int dtyp
   if (M <= 0) return 0;
   LEB_REQUIRE(E >= 1 && E <= MOE_MAX_E, "leb_moe_router: %d experts outside 1..%d", E, MOE_MAX_E);
   LEB_REQUIRE(k >= 1 && k <= MOE_MAX_K && k <= E, "leb_moe_router: top-%d outside 1..min(%d, experts)", k, MOE_MAX_K);
-  // rows per block: 4 when there are many rows and they fit shared memory, else 1
-  const bool four = M >= 8 && ((size_t)4 * D + 8 * E) * sizeof(float) <= 48 * 1024;
+  // rows per block: 1 while every row can have an SM of its own (a block's pace is set by one SM
+  // reading the router's weights), 4 for many rows when they fit shared memory
+  const bool four = M > 148 && ((size_t)4 * D + 8 * E) * sizeof(float) <= 48 * 1024;
   const int R = four ? 4 : 1;
   const size_t smem = ((size_t)R * D + 2 * R * E) * sizeof(float);
   LEB_REQUIRE(smem <= 48 * 1024, "leb_moe_router: hidden size %d too large for the router kernel", D);
@@ -139,49 +140,72 @@ LEB_API int leb_moe_router(int* topk_ids, float* topk_w, const void* h, int dtyp
 // Expert-sorted order of the P = M*k pairs (pair p = token p/k, choice p%k), stable in p:
 //   offsets[e] .. offsets[e+1]  rows of expert e in the sorted order
 //   sorted_pair[row] = p,  pair_row[p] = row
-// One block; warp w owns experts w, w+32, ... and walks the pairs in order with a ballot, so the
-// order is fixed without atomics.
-__global__ void moe_align_kernel(int* __restrict__ offsets, int* __restrict__ sorted_pair,
-                                 int* __restrict__ pair_row, const int* __restrict__ topk_ids,
-                                 int P, int E) {
-  __shared__ int counts[MOE_MAX_E + 1];
+// One block of 32 warps, a counting sort without atomics: warp w owns the pairs of chunk w (in
+// order), counts them per expert with __match_any_sync (lanes with the same expert find each other;
+// the first of them adds their number), the counts are turned into the first row of every
+// (warp, expert), and a second walk gives every pair its row: first row + pairs of the same
+// expert before it.  The order within an expert is the order of the pairs, run after run.
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(int* __restrict__ offsets, int* __restrict__ sorted_pair, int* __restrict__ pair_row,
+                 const int* __restrict__ topk_ids, int P, int E) {
+  __shared__ int cnt[32][MOE_MAX_E];
   pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nw) {
-    int cnt = 0;
-    for (int p0 = 0; p0 < P; p0 += 32) {
-      int p = p0 + lane;
-      bool mine = p < P && topk_ids[p] == e;
-      cnt += __popc(__ballot_sync(0xffffffffu, mine));
-    }
-    if (lane == 0) counts[e] = cnt;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = ((P + 31) / 32 + 31) / 32 * 32;   // pairs per warp, a multiple of 32
+  const int lo = warp * chunk, hi = min(P, lo + chunk);
+  for (int e = lane; e < E; e += 32) cnt[warp][e] = 0;
+  __syncwarp();
+  for (int p0 = lo; p0 < hi; p0 += 32) {
+    const int p = p0 + lane;
+    const bool valid = p < hi;
+    const int id = valid ? topk_ids[p] : -1 - lane;   // lanes past the end match nobody
+    const unsigned same = __match_any_sync(0xffffffffu, id);
+    if (valid && lane == __ffs(same) - 1) cnt[warp][id] += __popc(same);
+    __syncwarp();
+  }
+  __syncthreads();
+  // thread e: the experts' totals, then (thread 0) their first rows, then the first row of each warp's share
+  __shared__ int first[MOE_MAX_E + 1];
+  if ((int)threadIdx.x < E) {
+    int t = 0;
+    for (int w = 0; w < 32; w++) t += cnt[w][threadIdx.x];
+    first[threadIdx.x] = t;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
     for (int e = 0; e < E; e++) {
-      int c = counts[e];
-      counts[e] = run;
+      const int c = first[e];
+      first[e] = run;
       offsets[e] = run;
       run += c;
     }
-    counts[E] = run;
+    first[E] = run;
     offsets[E] = run;
   }
   __syncthreads();
-  for (int e = warp; e < E; e += nw) {
-    int base = counts[e];
-    for (int p0 = 0; p0 < P; p0 += 32) {
-      int p = p0 + lane;
-      bool mine = p < P && topk_ids[p] == e;
-      unsigned mask = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        int row = base + __popc(mask & ((1u << lane) - 1u));
-        sorted_pair[row] = p;
-        pair_row[p] = row;
-      }
-      base += __popc(mask);
+  if ((int)threadIdx.x < E) {
+    int run = first[threadIdx.x];
+    for (int w = 0; w < 32; w++) {
+      const int c = cnt[w][threadIdx.x];
+      cnt[w][threadIdx.x] = run;
+      run += c;
     }
+  }
+  __syncthreads();
+  for (int p0 = lo; p0 < hi; p0 += 32) {
+    const int p = p0 + lane;
+    const bool valid = p < hi;
+    const int id = valid ? topk_ids[p] : -1 - lane;
+    const unsigned same = __match_any_sync(0xffffffffu, id);
+    if (valid) {
+      const int row = cnt[warp][id] + __popc(same & ((1u << lane) - 1u));
+      sorted_pair[row] = p;
+      pair_row[p] = row;
+    }
+    __syncwarp();   // everyone has read its first row before the first of each expert moves it on
+    if (valid && lane == __ffs(same) - 1) cnt[warp][id] += __popc(same);
+    __syncwarp();
   }
 }
 
