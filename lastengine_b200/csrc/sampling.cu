@@ -131,20 +131,125 @@ LEB_API int leb_argmax(int* out, const float* logits, int n, int V, cudaStream_t
   return 0;
 }
 
-// Top-k by radix selection on the 64-bit (value, id) keys, a bitonic sort of the k winners, then
-// the reference's serial tail on one thread (at most 256 elements).
+// descending bitonic sort of n (a power of two) 64-bit keys in shared memory, by the whole block
+__device__ __forceinline__ void sort_keys_desc(unsigned long long* a, int n) {
+  for (int size = 2; size <= n; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < n; t += blockDim.x) {
+        const int j = t ^ stride;
+        if (j > t) {
+          const bool desc = (t & size) == 0;
+          const unsigned long long x = a[t], y = a[j];
+          if (desc ? x < y : x > y) { a[t] = y; a[j] = x; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// The k largest (value, id) keys of the row, sorted, then the reference's serial tail on one thread
+// (at most 256 elements).  Fast way: every thread takes the largest key of its share of the row;
+// the k-th largest of those 1024 maxima is a bound that at least k keys reach, and in a row that
+// is not laid out against it few more than k do: the keys that reach it are gathered in shared
+// memory and sorted.  If more than 1024 keys reach the bound, the k-th largest key is found by
+// radix selection over the whole row instead (eight passes), as slow as it is sure.
 __global__ void __launch_bounds__(SMP_THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ u01,
               int V, int k, float temperature, float top_p, float min_p) {
   __shared__ unsigned hist[256];
   __shared__ unsigned long long prefix_s;
   __shared__ int want_s;
+  __shared__ unsigned long long list[SMP_THREADS];
   __shared__ unsigned long long cand[SMP_MAX_K];
   __shared__ float prob[SMP_MAX_K];
-  __shared__ int n_cand;
+  __shared__ int n_cand, n_list;
+  __shared__ unsigned long long bound_s;
+  pdl_wait();
   const float* l = logits + (size_t)blockIdx.x * V;
   const int tid = threadIdx.x;
 
+  // a thread's share of the row: pieces of four values, 1024 pieces apart (single values if the row
+  // cannot be read in 16-byte pieces); several loads are in flight at a time
+  const bool vec = (V & 3) == 0 && ((uintptr_t)l & 15) == 0;
+  unsigned long long mine = 0ull;
+  if (vec) {
+    const float4* l4 = reinterpret_cast<const float4*>(l);
+#pragma unroll 8
+    for (int i = tid; i < V / 4; i += SMP_THREADS) {
+      const float4 v = l4[i];
+      const unsigned long long k0 = order_key(v.x, 4 * i), k1 = order_key(v.y, 4 * i + 1), k2 = order_key(v.z, 4 * i + 2),
+                               k3 = order_key(v.w, 4 * i + 3);
+      const unsigned long long a = k0 > k1 ? k0 : k1, b = k2 > k3 ? k2 : k3, c = a > b ? a : b;
+      mine = c > mine ? c : mine;
+    }
+  } else {
+#pragma unroll 8
+    for (int i = tid; i < V; i += SMP_THREADS) {
+      const unsigned long long key = order_key(l[i], i);
+      mine = key > mine ? key : mine;
+    }
+  }
+  // the largest key of each four neighbouring threads: 256 maxima, of which the k-th largest is
+  // found by counting, for each, how many are larger (no sorting, one barrier)
+#pragma unroll
+  for (int o = 1; o <= 2; o <<= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+    mine = other > mine ? other : mine;
+  }
+  if ((tid & 3) == 0) list[tid >> 2] = mine;
+  if (tid == 0) { n_list = 0; bound_s = 0ull; }
+  __syncthreads();
+  if (tid < 256) {
+    const unsigned long long key = list[tid];
+    int larger = 0;
+#pragma unroll 8
+    for (int j = 0; j < 256; j++) larger += list[j] > key ? 1 : 0;
+    if (larger == k - 1) bound_s = key;   // empty shares have key 0: with fewer than k others the bound stays 0
+  }
+  __syncthreads();
+  const unsigned long long bound = bound_s;   // at least k keys of the row are >= bound
+  __syncthreads();
+  auto reach = [&](unsigned long long key) {
+    if (key >= bound) {
+      const int p = atomicAdd(&n_list, 1);
+      if (p < SMP_THREADS) list[p] = key;
+    }
+  };
+  if (vec) {
+    const float4* l4 = reinterpret_cast<const float4*>(l);
+#pragma unroll 8
+    for (int i = tid; i < V / 4; i += SMP_THREADS) {
+      const float4 v = l4[i];
+      reach(order_key(v.x, 4 * i));
+      reach(order_key(v.y, 4 * i + 1));
+      reach(order_key(v.z, 4 * i + 2));
+      reach(order_key(v.w, 4 * i + 3));
+    }
+  } else {
+#pragma unroll 8
+    for (int i = tid; i < V; i += SMP_THREADS) reach(order_key(l[i], i));
+  }
+  __syncthreads();
+  const int reached = n_list;
+  if (reached <= 256) {
+    // few keys reached the bound (the usual case): each finds its place by counting the larger ones
+    if (tid < reached) {
+      const unsigned long long key = list[tid];
+      int larger = 0;
+      for (int j = 0; j < reached; j++) larger += list[j] > key ? 1 : 0;
+      if (larger < k) cand[larger] = key;
+    }
+    __syncthreads();
+  } else if (reached <= SMP_THREADS) {
+    int n = 2;
+    while (n < reached) n <<= 1;
+    for (int i = reached + tid; i < n; i += blockDim.x) list[i] = 0ull;
+    __syncthreads();
+    sort_keys_desc(list, n);
+    for (int i = tid; i < SMP_MAX_K; i += blockDim.x) cand[i] = i < k ? list[i] : 0ull;
+    __syncthreads();
+  } else {
   // k-th largest key: fix its bytes from the top
   if (tid == 0) { prefix_s = 0ull; want_s = k; n_cand = 0; }
   __syncthreads();
@@ -182,19 +287,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const flo
   for (int i = tid; i < SMP_MAX_K; i += blockDim.x)
     if (i >= k) cand[i] = 0ull;
   __syncthreads();
-  // bitonic sort, descending, of SMP_MAX_K keys
-  for (int size = 2; size <= SMP_MAX_K; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      if (tid < SMP_MAX_K) {
-        int j = tid ^ stride;
-        if (j > tid) {
-          bool desc = (tid & size) == 0;
-          unsigned long long a = cand[tid], c = cand[j];
-          if (desc ? a < c : a > c) { cand[tid] = c; cand[j] = a; }
-        }
-      }
-      __syncthreads();
-    }
+  sort_keys_desc(cand, SMP_MAX_K);
   }
   if (tid == 0) {
     auto logit_of = [&](int i) { return l[(int)(0xffffffffu - (unsigned)(cand[i] & 0xffffffffull))]; };
@@ -239,7 +332,7 @@ LEB_API int leb_sample(int* out, const float* logits, const float* u01, int n, i
   int k = top_k == 0 ? 64 : (top_k < SMP_MAX_K ? top_k : SMP_MAX_K);  // src/local.rs:65
   if (k > V) k = V;
   LEB_REQUIRE(k >= 1, "leb_sample: empty vocabulary");
-  sample_kernel<<<n, SMP_THREADS, 0, st>>>(out, logits, u01, V, k, temperature, top_p, min_p);
+  leb_launch(sample_kernel, dim3(n), dim3(SMP_THREADS), 0, st, out, logits, u01, V, k, temperature, top_p, min_p);
   LEB_CHECK_LAUNCH("leb_sample");
   return 0;
 }
