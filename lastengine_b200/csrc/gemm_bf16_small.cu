@@ -17,13 +17,6 @@
 // [off[e], off[e+1]), weights W + e*w_group_stride).  epilogue: 0 store, 1 add into float C,
 // 2 SwiGLU over interleaved weights (rows 32j..32j+15 gate, 32j+16..32j+31 up of the same 16
 // outputs): C[m, 16j+i] = silu(gate_i) * up_i, so C has N/2 columns.
-//
-// NORM: the left operand is RMSNorm(x) of the float residual x, formed on the fly
-// (src/dense.rs:27-30: x / sqrt(mean(x^2) + eps) * w): the block first sums the squares of its
-// rows (one warp per row; its weight rows were asked into L2 before that), then builds
-// each bfloat16 fragment as bf16(x * r * w), the value the separate norm kernel would have
-// stored.  This takes the norm's launch and its round trip through memory out of every
-// matrix product of a decode step.
 #include "common.cuh"
 
 #define SM_WARPS 8
@@ -39,14 +32,12 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a
 }
 
 // MT tiles of 8 activation rows, NSUB tiles of 16 weight rows, U k-slices of a warp loaded at once
-template <typename TC, int MT, int NSUB, int U, bool NORM>
+template <typename TC, int MT, int NSUB, int U>
 __global__ void __launch_bounds__(32 * SM_WARPS)
 gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
                        int M, int N, int K, int lda, int ldc, int epilogue,
-                       const int* __restrict__ group_offsets, size_t w_group_stride,
-                       const float* __restrict__ xres, const float* __restrict__ norm_w, float eps) {
+                       const int* __restrict__ group_offsets, size_t w_group_stride) {
   __shared__ float red[SM_WARPS][NSUB][SM_ROWS][8 * MT + 1];
-  __shared__ float rnorm[8 * MT];
   int row_begin = 0, row_end = M;
   const int n0 = blockIdx.x * (SM_ROWS * NSUB);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -91,25 +82,9 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
 #pragma unroll
   for (int t = 0; t < MT; t++) {
     int m = m0 + t * 8 + r;
-    arow[t] = (!NORM && m < row_end) ? A + (size_t)m * lda : nullptr;
+    arow[t] = m < row_end ? A + (size_t)m * lda : nullptr;
   }
 
-  if (NORM) {
-    // r = 1 / sqrt(mean(x^2) + eps) per row: warp w takes rows w, w+8, ...; lda is x's row stride
-    for (int m = warp; m < 8 * MT; m += SM_WARPS) {
-      float ss = 0.f;
-      if (m0 + m < row_end) {
-        const float4* xr = reinterpret_cast<const float4*>(xres + (size_t)(m0 + m) * lda);
-        for (int i = lane; i < K / 4; i += 32) {
-          const float4 v = xr[i];
-          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) rnorm[m] = 1.0f / sqrtf(ss / (float)K + eps);
-    }
-    __syncthreads();
-  }
   const int n_kb = (K + 31) / 32;
   // The stream is only as fast as the bytes in flight: a warp first issues the loads of U of
   // its k-slices (U * (2 NSUB + MT) 16-byte loads per lane), and only then multiplies.  A deep
@@ -127,28 +102,8 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
         wa[u][s][0] = kin ? __ldg((const uint4*)(wrow[s][0] + k)) : zero;
         wa[u][s][1] = kin ? __ldg((const uint4*)(wrow[s][1] + k)) : zero;
       }
-      if (NORM) {
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-          xb[u][t] = zero;
-          const int m = m0 + t * 8 + r;
-          if (kin && m < row_end) {
-            const float4* xr = reinterpret_cast<const float4*>(xres + (size_t)m * lda + k);
-            const float4* wr = reinterpret_cast<const float4*>(norm_w + k);
-            const float4 a0 = xr[0], a1 = xr[1], w0 = wr[0], w1 = wr[1];
-            const float rr = rnorm[t * 8 + r];
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(a0.x * rr * w0.x, a0.y * rr * w0.y);
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(a0.z * rr * w0.z, a0.w * rr * w0.w);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(a1.x * rr * w1.x, a1.y * rr * w1.y);
-            __nv_bfloat162 p3 = __floats2bfloat162_rn(a1.z * rr * w1.z, a1.w * rr * w1.w);
-            xb[u][t] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                                  *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
-          }
-        }
-      } else {
-#pragma unroll
-        for (int t = 0; t < MT; t++) xb[u][t] = (kin && arow[t]) ? *(const uint4*)(arow[t] + k) : zero;
-      }
+      for (int t = 0; t < MT; t++) xb[u][t] = (kin && arow[t]) ? *(const uint4*)(arow[t] + k) : zero;
     }
 #pragma unroll
     for (int u = 0; u < U; u++)
@@ -206,8 +161,7 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
 template <typename TC, int NSUB>
 static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int K, int lda, int ldc,
                         int epilogue, const int* group_offsets, int n_groups, size_t w_group_stride,
-                        int rows_hint, cudaStream_t st, const float* xres = nullptr,
-                        const float* norm_w = nullptr, float eps = 0.f) {
+                        int rows_hint, cudaStream_t st) {
   // rows_hint: the most rows one group can have (M without groups)
   int mt = rows_hint <= 8 ? 1 : (rows_hint <= 16 ? 2 : (rows_hint <= 32 ? 4 : 8));
   if (NSUB == 2 && mt == 8) mt = 4;  // shared memory of the reduction
@@ -215,18 +169,8 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
   if (grid.y > 65535 || grid.z > 65535) return leb_fail("leb_gemm_bf16_small: grid too large");
   dim3 block(32 * SM_WARPS);
 #define LEB_SM(MT_, U_)                                                                          \
-  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB, U_, false>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, \
-             ldc, epilogue, group_offsets, w_group_stride, (const float*)nullptr, (const float*)nullptr, 0.f)
-#define LEB_SMN(MT_, U_)                                                                         \
-  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB, U_, true>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda,  \
-             ldc, epilogue, group_offsets, w_group_stride, xres, norm_w, eps)
-  if (xres) {   // the fused norm: few rows only
-    if (mt == 1) LEB_SMN(1, 4);
-    else if (mt == 2) LEB_SMN(2, 2);
-    else return leb_fail("leb_gemm_bf16_small: the fused norm takes at most 16 rows");
-    LEB_CHECK_LAUNCH("leb_gemm_bf16_small");
-    return 0;
-  }
+  leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB, U_>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, \
+             ldc, epilogue, group_offsets, w_group_stride)
   switch (mt) {
     case 1: {
       // blocks resident per SM for each depth (asked once), and the SM count
@@ -235,9 +179,9 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[0], gemm_bf16_small_kernel<TC, 1, NSUB, 8, false>, 32 * SM_WARPS, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[1], gemm_bf16_small_kernel<TC, 1, NSUB, 4, false>, 32 * SM_WARPS, 0);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[2], gemm_bf16_small_kernel<TC, 1, NSUB, 2, false>, 32 * SM_WARPS, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[0], gemm_bf16_small_kernel<TC, 1, NSUB, 8>, 32 * SM_WARPS, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[1], gemm_bf16_small_kernel<TC, 1, NSUB, 4>, 32 * SM_WARPS, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[2], gemm_bf16_small_kernel<TC, 1, NSUB, 2>, 32 * SM_WARPS, 0);
         if (n_sm <= 0) n_sm = 148;
       }
       const long blocks = (long)grid.x * grid.y * grid.z;
@@ -253,7 +197,6 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
       break;
   }
 #undef LEB_SM
-#undef LEB_SMN
   LEB_CHECK_LAUNCH("leb_gemm_bf16_small");
   return 0;
 }
@@ -284,25 +227,4 @@ LEB_API int leb_gemm_bf16_small(void* C, int c_dtype, const void* A, const void*
       return launch_small<float, 1>(C, a, w, M, N, K, lda, ldc, epilogue, group_offsets, n_groups, w_group_stride, rows_hint, st);
   }
   return leb_fail("leb_gemm_bf16_small: unknown C dtype %d", c_dtype);
-}
-
-// The same product with RMSNorm(x) as the left operand: x is the float residual [M, K] with row
-// stride ldx, norm_w the norm's weight [K].  At most 16 rows; no groups.
-LEB_API int leb_gemm_bf16_small_norm(void* C, int c_dtype, const float* x, int ldx, const float* norm_w, float eps,
-                                     const void* W, int M, int N, int K, int ldc, int epilogue, cudaStream_t st) {
-  if (M <= 0 || N <= 0) return 0;
-  LEB_REQUIRE(M <= 16, "leb_gemm_bf16_small_norm: %d rows; the fused norm takes at most 16", M);
-  LEB_REQUIRE(K > 0 && K % 8 == 0 && ldx % 4 == 0, "leb_gemm_bf16_small_norm: K (%d) must be a multiple of 8 and the row stride (%d) of 4", K, ldx);
-  LEB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)norm_w & 15) == 0 && ((uintptr_t)W & 15) == 0, "leb_gemm_bf16_small_norm: operands must be 16-byte aligned");
-  LEB_REQUIRE(epilogue == 0 || epilogue == 2, "leb_gemm_bf16_small_norm: epilogue %d not taken (store or SwiGLU)", epilogue);
-  const bf16* w = (const bf16*)W;
-  if (epilogue == 2) {
-    LEB_REQUIRE(N % 32 == 0, "leb_gemm_bf16_small_norm: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
-    if (c_dtype == LEB_BF16) return launch_small<bf16, 2>(C, nullptr, w, M, N, K, ldx, ldc, 2, nullptr, 1, 0, M, st, x, norm_w, eps);
-    if (c_dtype == LEB_F32) return launch_small<float, 2>(C, nullptr, w, M, N, K, ldx, ldc, 2, nullptr, 1, 0, M, st, x, norm_w, eps);
-  } else {
-    if (c_dtype == LEB_BF16) return launch_small<bf16, 1>(C, nullptr, w, M, N, K, ldx, ldc, 0, nullptr, 1, 0, M, st, x, norm_w, eps);
-    if (c_dtype == LEB_F32) return launch_small<float, 1>(C, nullptr, w, M, N, K, ldx, ldc, 0, nullptr, 1, 0, M, st, x, norm_w, eps);
-  }
-  return leb_fail("leb_gemm_bf16_small_norm: unknown C dtype %d", c_dtype);
 }

@@ -43,7 +43,6 @@ def _declare(L) -> None:
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
         "leb_gemm_bf16_stream_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_tc_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
-        "leb_gemm_bf16_small_norm": [P, I, P, I, P, F, P, I, I, I, I, I, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
         "leb_moe_align": [P, P, P, P, I, I, P],
         "leb_moe_combine": [P, P, P, P, I, I, I, I, P],
@@ -319,39 +318,13 @@ STORE, ACCUMULATE, SWIGLU = 0, 1, 2
 SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcgen05 tiles
 
 
-# Forming the norm inside the product saves a launch per product but puts the sum of squares in
-# front of every block's weight stream; measured on B200 (hidden 2048, batch 1 and 8) a decode
-# step got 10% slower, so it is off.  The path stays tested.  (The same was measured for the norm
-# formed in the tail of the product before it, by the block that finishes last, and for the norm
-# inside the ring-fed kernel: with programmatic dependent launch the small norm kernel between two
-# products is the window in which the next product starts up and prefetches its weights, so
-# taking it out saves nothing.)
-FUSE_NORM = False
+# Forming the norm inside a product (in the consumer's prologue, or in the tail of the product
+# before it) was built and measured slower than the separate norm kernel each time: with
+# programmatic dependent launch the small norm kernel between two products is the window in which
+# the next product starts up and fetches its first weights.  So the norm stays a kernel of its own.
 
 
-class NormedInput:
-    """RMSNorm(x) that has not been computed yet: the float residual rows `x`, the norm's weight
-    and eps.  `linear` forms it inside the matrix product when it can (bfloat16, few rows);
-    `materialize` runs the norm kernel into `buf` for everything else."""
-
-    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, buf: torch.Tensor):
-        self.x, self.weight, self.eps, self.buf = x, weight, eps, buf
-        self._done = False
-        self.shape, self.dtype, self.device = buf.shape, buf.dtype, buf.device
-
-    def materialize(self) -> torch.Tensor:
-        if not self._done:
-            rmsnorm(self.buf, self.x, self.weight, self.eps)
-            self._done = True
-        return self.buf
-
-
-def as_tensor(h) -> torch.Tensor:
-    """The activation tensor of `h`, computing a pending norm if there is one."""
-    return h.materialize() if isinstance(h, NormedInput) else h
-
-
-def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
            group_offsets: torch.Tensor | None = None, rows_hint: int = 0, streaming: bool = False) -> None:
     """out (+)= x . w^T  with w [N, K] (or [E, N, K] with group_offsets [E+1] over the rows).
 
@@ -362,20 +335,6 @@ def linear(out: torch.Tensor, x, w: torch.Tensor, epilogue: int = STORE,
     with more rows they go to the tcgen05 kernels; `streaming` asks for the register-fed
     weight-streaming kernel (the one that also serves grouped products) whatever the row count.
     """
-    if isinstance(x, NormedInput):
-        nx = x
-        M, K = nx.shape
-        if (not nx._done and nx.dtype == torch.bfloat16 and M <= SMALL_M and group_offsets is None
-                and epilogue in (STORE, SWIGLU) and K % 8 == 0 and nx.x.stride(0) % 4 == 0):
-            _cuda(w, "linear.w", torch.bfloat16)
-            _cuda(out, "linear.out", contiguous=False)
-            N = w.shape[0]
-            assert w.shape[1] == K and out.shape == (M, N // 2 if epilogue == SWIGLU else N)
-            _check(lib().leb_gemm_bf16_small_norm(_ptr(out), _dt(out, "linear.out"), _ptr(nx.x), nx.x.stride(0),
-                                                  _ptr(nx.weight), float(nx.eps), _ptr(w), M, N, K, out.stride(0),
-                                                  epilogue, _stream()))
-            return
-        x = nx.materialize()
     _cuda(x, "linear.x", contiguous=False)
     _cuda(w, "linear.w", x.dtype)
     _cuda(out, "linear.out", contiguous=False)

@@ -20,7 +20,6 @@ from .base import MATRIX, NORM, BuildEnv, KVSpec, Mixer, PartSpec, TensorSpec
 
 @MIXERS.register("attention")
 class AttentionMixer(Mixer):
-    takes_pending_norm = True      # its first product may form norm(x) itself
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  norm_eps: float, qk_norm: bool = True, position: PartSpec | None = None,
                  window: int = 0, output_gate: bool = False, own_kv: bool = True,

@@ -28,27 +28,19 @@ class PreNormResidualBlock:
             p["post_ffn_norm"] = self.post_ffn_norm
         return p
 
-    @staticmethod
-    def _normed(norm, part, x, buf):
-        """The part's input norm(x): computed now, or, for parts that say they take it, handed on
-        as a pending norm that their first matrix product forms on the fly (decode steps)."""
-        if (kernels.FUSE_NORM and getattr(part, "takes_pending_norm", False) and hasattr(norm, "weight")
-                and hasattr(norm, "eps")):
-            return kernels.NormedInput(x, norm.weight, norm.eps, buf)
-        norm.forward(buf, x)
-        return buf
-
     def forward(self, x: torch.Tensor, batch, cache, env) -> None:
         M, D = x.shape
         ws = env.workspace
-        h = self._normed(self.mixer_norm, self.mixer, x, ws.get("block.h", (M, D), env.dtype))
+        h = ws.get("block.h", (M, D), env.dtype)
+        self.mixer_norm.forward(h, x)
         if self.post_mixer_norm is None:
             self.mixer.forward(h, x, True, batch, cache, env)
         else:
             t = ws.get("block.t", (M, D), torch.float32)
             self.mixer.forward(h, t, False, batch, cache, env)
             self.post_mixer_norm.forward(x, t, add=True)
-        h = self._normed(self.ffn_norm, self.ffn, x, ws.get("block.h", (M, D), env.dtype))
+        h = ws.get("block.h", (M, D), env.dtype)
+        self.ffn_norm.forward(h, x)
         if self.post_ffn_norm is None:
             self.ffn.forward(h, x, True, batch, env)
         else:

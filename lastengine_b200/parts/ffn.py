@@ -33,7 +33,6 @@ def fuse_gate_up(w1: torch.Tensor, w3: torch.Tensor, interleave: bool) -> torch.
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    takes_pending_norm = True      # its first product may form norm(x) itself
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.D, self.F = int(hidden_size), int(intermediate_size)
         self.w13 = self.w2 = None

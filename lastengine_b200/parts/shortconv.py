@@ -15,7 +15,6 @@ from .base import MATRIX, VECTOR, BuildEnv, Mixer, StateSpec, TensorSpec
 
 @MIXERS.register("shortconv")
 class ShortConvMixer(Mixer):
-    takes_pending_norm = True      # its first product may form norm(x) itself
     def __init__(self, hidden_size: int, L_cache: int):
         if not 2 <= L_cache <= 17:
             raise ValueError(f"conv_L_cache {L_cache} outside what the kernel takes (2..17)")
