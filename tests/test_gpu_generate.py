@@ -10,7 +10,7 @@ import torch
 
 import harness as H
 import plain_lfm3 as P
-from tiny_configs import TINY_A, TINY_B
+from tiny_configs import TINY_A, TINY_B, TINY_C
 
 pytestmark = pytest.mark.gpu
 
@@ -98,6 +98,29 @@ def test_stop_tokens_end_requests_early(dirs):
     sp = SamplingParams(temperature=0.9, seed=5)
     assert eng.generate(prompts, sp, max_new_tokens=10, stop_token_ids=[stop]).tokens == \
         eng.generate(prompts, sp, max_new_tokens=10, stop_token_ids=[stop], use_graphs=False).tokens
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_with_a_window_and_early_stops(dtype, tmp_path):
+    """The configuration with a sliding window (its pages come and go, so every decode step is staged
+    in full), head gate and sandwich norms: generation with steps launched ahead of the host gives
+    the tokens of generation step by step, with requests that stop at different times, and with
+    a batch limit that makes slots come round again."""
+    from lastengine_b200 import Engine, SamplingParams
+    eng = Engine.from_pretrained(H.make_model_dir(TINY_C, 2, str(tmp_path)), dtype=dtype, max_tokens=2048)
+    prompts = H.requests_for(TINY_C, [3, 19, 40, 7, 90], 31)
+    greedy = SamplingParams(temperature=0.0)
+    free = eng.generate(prompts, greedy, max_new_tokens=24, stop_token_ids=[], use_graphs=False)
+    stops = [free.tokens[1][5], free.tokens[3][11]]
+    for sp in (greedy, SamplingParams(temperature=0.9, top_k=20, seed=4)):
+        slow = eng.generate(prompts, sp, max_new_tokens=24, stop_token_ids=stops, use_graphs=False)
+        fast = eng.generate(prompts, sp, max_new_tokens=24, stop_token_ids=stops)
+        assert fast.tokens == slow.tokens and fast.finish_reasons == slow.finish_reasons
+        assert "stop" in fast.finish_reasons and len({len(t) for t in fast.tokens}) > 1     # they end at different times
+        two = eng.generate(prompts, sp, max_new_tokens=24, stop_token_ids=stops, max_batch=2)
+        assert two.tokens == slow.tokens and two.stats.batches == 3
+    assert eng.cache.slots.n_held == 0
+    eng.cache.check()
 
 
 def run_trace(model_dir, dtype, steps, out_dir, max_tokens=1024):
