@@ -126,7 +126,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     for (int i = 0; i < 2; i++) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 4);
       mbar_init(&pv_done[i], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -214,24 +214,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tmem_ld_wait();
       // columns [c_lo, c_hi] of this page are keys this row may see
       const int c_lo = max(0, key_lo_row - key0), c_hi = row_valid ? min(PAGE - 1, qpos - key0) : -1;
+      // The scores stay as the product left them; the scale goes into the exponent's multiply-add.
       float rm[4] = {ATC_NEG, ATC_NEG, ATC_NEG, ATC_NEG};   // four chains instead of one of 64 steps
       if (c_lo == 0 && c_hi == PAGE - 1) {
 #pragma unroll
-        for (int c = 0; c < PAGE; c++) {
-          const float sc = __uint_as_float(v[c]) * scale2;
-          v[c] = __float_as_uint(sc);
-          rm[c & 3] = fmaxf(rm[c & 3], sc);
-        }
+        for (int c = 0; c < PAGE; c++) rm[c & 3] = fmaxf(rm[c & 3], __uint_as_float(v[c]));
       } else {
 #pragma unroll
         for (int c = 0; c < PAGE; c++) {
-          const float sc = (c >= c_lo && c <= c_hi) ? __uint_as_float(v[c]) * scale2 : ATC_NEG;
+          const float sc = (c >= c_lo && c <= c_hi) ? __uint_as_float(v[c]) : ATC_NEG;
           v[c] = __float_as_uint(sc);
           rm[c & 3] = fmaxf(rm[c & 3], sc);
         }
       }
       const float rmax = fmaxf(fmaxf(rm[0], rm[1]), fmaxf(rm[2], rm[3]));
-      const float m_new = fmaxf(m_used, rmax);
+      // maxima are kept times scale * log2(e); a row with no key in this page keeps what it had
+      const float m_new = rmax > 0.5f * ATC_NEG ? fmaxf(m_used, rmax * scale2) : m_used;
       bool move = false;
       if (l == 0.f) m_used = m_new;                 // nothing accumulated for this row yet: O's row is zero
       else if (m_new > m_used + 8.f) move = true;   // the reference maximum has to follow
@@ -258,8 +256,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < PAGE; c += 2) {
-        // a masked score is -1e30: 2^(that - m_ref) is exactly zero
-        const float p0 = ex2(__uint_as_float(v[c]) - m_ref), p1 = ex2(__uint_as_float(v[c + 1]) - m_ref);
+        // a masked score is -1e30: 2^(that * scale - m_ref) is exactly zero
+        const float p0 = ex2(fmaf(__uint_as_float(v[c]), scale2, -m_ref)), p1 = ex2(fmaf(__uint_as_float(v[c + 1]), scale2, -m_ref));
         ps[(c >> 1) & 3] += p0 + p1;
         __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
@@ -284,7 +282,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         fence_proxy_async_smem();
       }
       tc_fence_before();
-      mbar_arrive(&p_full[bsel]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[bsel]);   // one arrival per softmax warp
     }
     if (ok) {
       if (!mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag)) { atomicExch(status, 20); ok = false; }
