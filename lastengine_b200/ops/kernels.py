@@ -43,6 +43,7 @@ def _declare(L) -> None:
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
         "leb_gemm_bf16_stream_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_tc_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
+        "leb_gemm_bf16_tc2": [P, I, P, P, I, I, I, I, I, I, P, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
         "leb_moe_align": [P, P, P, P, I, I, P],
         "leb_moe_combine": [P, P, P, P, I, I, I, I, P],
@@ -377,6 +378,9 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
     if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296
             and linear_skinny(out, x, w, epilogue)):
         return
+    if (not streaming and group_offsets is None and M >= PAIRS_MIN_ROWS and (N >= 4096 or K >= 4096)
+            and linear_tc2(out, x, w, epilogue)):
+        return      # many rows and a large weight matrix: 256 x 256 tiles on pairs of SMs
     if tc is not None and not streaming and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
         return
     if (not streaming and group_offsets is not None and E <= 256 and M > 16 * E and w.is_contiguous()
@@ -518,6 +522,21 @@ def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int
         return False
     _check(L.leb_gemm_bf16_tc(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                               out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
+    return True
+
+
+PAIRS_MIN_ROWS = 1024   # rows from which the paired kernel is used (measured: 3-9% faster there, slower on small products)
+
+
+def linear_tc2(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE) -> bool:
+    """out (+)= x . w^T on pairs of SMs (tcgen05 cta_group::2, 256 x 256 tiles); False when the operands cannot go through TMA."""
+    L = lib()
+    M, K = x.shape
+    N = w.shape[0]
+    if not L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, x.stride(0)):
+        return False
+    _check(L.leb_gemm_bf16_tc2(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
+                               out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
     return True
 
 

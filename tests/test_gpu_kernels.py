@@ -664,6 +664,33 @@ def test_shortconv_kernels_against_the_references_own():
             assert err(state[2], torch.from_numpy(g[f"state_out{case}"])) < 1e-6, (case, mode)
 
 
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 64), (300, 520, 136), (129, 100, 72), (1000, 2048, 5632), (2048, 6144, 2048)])
+def test_linear_tc_pairs(M, N, K_):
+    """The product on pairs of SMs (cta_group::2, 256 x 256 tiles): tile-aligned sizes and sizes where
+    rows, columns and k run past the last tile; store, add to the residual, SwiGLU, both result types."""
+    x, w = gen(M, K_, seed=100, dtype=torch.bfloat16), gen(N, K_, seed=101, scale=0.05, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    assert K().linear_tc2(out, x.to(DEV), w.to(DEV))
+    K().check_device_status()
+    assert err(out, want) < 2e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear_tc2(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=102).to(DEV)
+    b0 = base.clone()
+    K().linear_tc2(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert err(base, b0.cpu().double() + want) < 2e-5
+    if N % 32 == 0:
+        from lastengine_b200.parts.ffn import fuse_gate_up
+        F = N // 2
+        w13 = fuse_gate_up(w[:F], w[F:], True).to(DEV)
+        o2 = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+        K().linear_tc2(o2, x.to(DEV), w13, K().SWIGLU)
+        assert err(o2, P.silu(want[:, :F]) * want[:, F:]) < 6e-3
+    K().check_device_status()
+
+
 @pytest.mark.parametrize("M,N,K_", [(17, 2048, 2048), (64, 352, 128), (100, 6144, 64), (33, 11264, 192), (128, 100, 200),
                                     (1, 128, 64), (16, 48, 72), (48, 2048, 5632), (64, 65536, 256)])
 def test_linear_skinny(M, N, K_):
