@@ -49,6 +49,64 @@ LEB_API int leb_penalties(float* logits, const int* hist, const int* hist_len, i
   return 0;
 }
 
+// The same penalties for steps that run without the host (captured decode steps): the recent tokens
+// of every sequence live in a ring per cache slot on the device, hist[slot][window], with
+// hist_len[slot] the number of tokens the sequence has seen so far.  The order in which a ring's
+// entries are applied does not matter: different tokens touch different logits, and the
+// occurrences of one token apply the same function again and again.
+__global__ void penalties_slots_kernel(float* __restrict__ logits, const int* __restrict__ hist,
+                                       const int* __restrict__ hist_len, const int* __restrict__ seq_slot,
+                                       int window, int V, int n, float repeat_penalty, float presence_penalty) {
+  pdl_wait();
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n) return;
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  float* l = logits + (size_t)b * V;
+  const int* h = hist + (size_t)slot * window;
+  const int len = min(hist_len[slot], window);
+  for (int i = 0; i < len; i++) {
+    int t = h[i];
+    if (t < 0 || t >= V) continue;
+    float v = l[t];
+    if (repeat_penalty > 1.0f) v = v > 0.f ? v / repeat_penalty : v * repeat_penalty;
+    l[t] = v - presence_penalty;
+  }
+}
+
+// The chosen token of every live sequence goes into its ring (over the oldest entry once it is full).
+__global__ void history_append_kernel(int* __restrict__ hist, int* __restrict__ hist_len,
+                                      const int* __restrict__ seq_slot, const int* __restrict__ chosen,
+                                      int window, int n) {
+  pdl_wait();
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n) return;
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  const int len = hist_len[slot];
+  hist[(size_t)slot * window + len % window] = chosen[b];
+  hist_len[slot] = len + 1;
+}
+
+LEB_API int leb_penalties_slots(float* logits, const int* hist, const int* hist_len, const int* seq_slot, int window,
+                                int n, int V, float repeat_penalty, float presence_penalty, cudaStream_t st) {
+  if (n <= 0) return 0;
+  LEB_REQUIRE(window > 0, "leb_penalties_slots: the window must be positive");
+  leb_launch(penalties_slots_kernel, dim3(ceil_div(n, 64)), dim3(64), 0, st, logits, hist, hist_len, seq_slot, window, V, n,
+             repeat_penalty, presence_penalty);
+  LEB_CHECK_LAUNCH("leb_penalties_slots");
+  return 0;
+}
+
+LEB_API int leb_history_append(int* hist, int* hist_len, const int* seq_slot, const int* chosen, int window, int n,
+                               cudaStream_t st) {
+  if (n <= 0) return 0;
+  LEB_REQUIRE(window > 0, "leb_history_append: the window must be positive");
+  leb_launch(history_append_kernel, dim3(ceil_div(n, 64)), dim3(64), 0, st, hist, hist_len, seq_slot, chosen, window, n);
+  LEB_CHECK_LAUNCH("leb_history_append");
+  return 0;
+}
+
 __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
   __shared__ unsigned long long best[32];
   const float* l = logits + (size_t)blockIdx.x * V;

@@ -15,7 +15,7 @@ import torch
 
 from ..cache import CacheFull
 from ..ops import kernels
-from ..sampling.params import SamplingParams
+from ..sampling.params import PENALTY_WINDOW, SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import BatchBuilder
 from .generate import EngineBackend
@@ -36,10 +36,12 @@ class DecodeGraph:
     that feed themselves) the move to the next position."""
 
     def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False,
-                 out: torch.Tensor | None = None, fed: bool = False):
+                 out: torch.Tensor | None = None, fed: bool = False, history=None):
         """`out`: where the chosen tokens go (shared between the buckets of one backend, so that a
         step of one bucket can take its tokens from the step of another).  `fed`: the step begins
-        by taking tokens from `out` where the staged step says so."""
+        by taking tokens from `out` where the staged step says so.  `history`: (ring of recent
+        tokens per cache slot [slots, 256], tokens seen per slot) on the device, for the penalties."""
+        self.history = history
         self.engine, self.sampler, self.bucket, self.width = engine, sampler, bucket, table_width
         self.self_feeding, self.fed = self_feeding, fed
         self.ws = Workspace(engine.device)
@@ -56,7 +58,13 @@ class DecodeGraph:
         if batch.feed is not None:
             kernels.feed_tokens(batch, self.out)
         logits = eng.model.forward(batch, eng.cache)
+        p = self.sampler.params
+        if p.has_penalties and self.history is not None:
+            kernels.penalties_slots(logits, self.history[0], self.history[1], batch.seq_slot, p.repeat_penalty,
+                                    p.presence_penalty)
         self.sampler.sample(self.out[:self.bucket], logits, batch.u01)
+        if p.has_penalties and self.history is not None:
+            kernels.history_append(self.history[0], self.history[1], batch.seq_slot, self.out, self.bucket)
         if self.self_feeding:
             kernels.advance(batch, self.out)
 
@@ -193,10 +201,21 @@ class GraphBackend(EngineBackend):
         out = self.graphs.get("out")
         if out is None or out.numel() < n:
             # graphs point at the old buffer: they are captured again with the new one
-            for k in [k for k in self.graphs if k != "out"]:
+            for k in [k for k in self.graphs if isinstance(k, int)]:
                 del self.graphs[k]
             out = self.graphs["out"] = torch.zeros(max(256, n), dtype=torch.int32, device=self.engine.device)
         return out
+
+    def _history(self):
+        """The rings of recent tokens per cache slot (made when the sampling has penalties)."""
+        if not self.sampler.params.has_penalties:
+            return None
+        h = self.graphs.get("history")
+        if h is None:
+            n = self.engine.cache.max_seqs
+            h = self.graphs["history"] = (torch.zeros((n, PENALTY_WINDOW), dtype=torch.int32, device=self.engine.device),
+                                          torch.zeros(n, dtype=torch.int32, device=self.engine.device))
+        return h
 
     def _launch(self, slots, tokens, u01, feed) -> _StepInFlight:
         eng = self.engine
@@ -204,7 +223,7 @@ class GraphBackend(EngineBackend):
         out = self._chosen(b)
         g = self.graphs.get(b)
         if g is None:
-            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width, out=out, fed=True)
+            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width, out=out, fed=True, history=self._history())
         grow = g.restage(slots, tokens, u01, feed)
         if grow is None:
             grow = g.stage(slots, tokens, u01, feed)
@@ -249,7 +268,22 @@ class GraphBackend(EngineBackend):
 
     def start(self, prompts, u01, histories):
         self._drain()
-        return super().start(prompts, u01, histories)
+        slots, toks = super().start(prompts, u01, histories)
+        h = self._history()
+        if h is not None:
+            # the rings of the new sequences: their last tokens, the first chosen one among them
+            rows = np.zeros((len(slots), PENALTY_WINDOW), dtype=np.int32)
+            lens = np.zeros(len(slots), dtype=np.int32)
+            for i, (p, t) in enumerate(zip(prompts, toks)):
+                seen = len(p) + 1
+                tail = (list(p) + [int(t)])[-PENALTY_WINDOW:]
+                for j, tok in enumerate(tail):              # token number q of the sequence lies at q % window
+                    rows[i, (seen - len(tail) + j) % PENALTY_WINDOW] = tok
+                lens[i] = seen
+            idx = torch.tensor(slots, dtype=torch.long, device=self.engine.device)
+            h[0][idx] = torch.from_numpy(rows).to(self.engine.device)
+            h[1][idx] = torch.from_numpy(lens).to(self.engine.device)
+        return slots, toks
 
     def finish(self, slots):
         if self._ahead is None:
@@ -263,9 +297,6 @@ class GraphBackend(EngineBackend):
     def decode(self, slots, tokens, u01, histories, lookahead=None):
         """`lookahead` = (the uniform numbers of the step after this one or None, for each slot
         whether its request can go on after this step's token)."""
-        if self.sampler.params.has_penalties:
-            self._drain()
-            return super().decode(slots, tokens, u01, histories)
         step, self._ahead = self._ahead, None
         if step is not None:
             place = {s: i for i, s in enumerate(step.slots)}

@@ -52,6 +52,8 @@ def _declare(L) -> None:
         "leb_sample": [P, P, P, I, I, I, F, F, F, P],
         "leb_advance": [P, P, P, P, P, I, P],
         "leb_feed_tokens": [P, P, P, I, P],
+        "leb_penalties_slots": [P, P, P, P, I, I, I, F, F, P],
+        "leb_history_append": [P, P, P, P, I, I, P],
         "leb_attention_decode_supported": [I, I, I, I],
         "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
@@ -452,6 +454,28 @@ def penalties(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Tensor,
     assert hist.shape[0] >= n
     _check(lib().leb_penalties(_ptr(logits), _ptr(hist), _ptr(hist_len), hist.shape[1], n, V,
                                float(repeat_penalty), float(presence_penalty), _stream()))
+
+
+def penalties_slots(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Tensor, seq_slot: torch.Tensor,
+                    repeat_penalty: float, presence_penalty: float) -> None:
+    """Penalises, in place, the tokens in each sequence's ring of recent tokens (hist [slots, window])."""
+    _cuda(logits, "penalties_slots.logits", torch.float32)
+    _cuda(hist, "penalties_slots.hist", torch.int32)
+    _cuda(hist_len, "penalties_slots.hist_len", torch.int32)
+    _cuda(seq_slot, "penalties_slots.seq_slot", torch.int32)
+    n, V = logits.shape
+    assert seq_slot.numel() >= n and hist_len.numel() == hist.shape[0]
+    _check(lib().leb_penalties_slots(_ptr(logits), _ptr(hist), _ptr(hist_len), _ptr(seq_slot), hist.shape[1], n, V,
+                                     float(repeat_penalty), float(presence_penalty), _stream()))
+
+
+def history_append(hist: torch.Tensor, hist_len: torch.Tensor, seq_slot: torch.Tensor, chosen: torch.Tensor, n: int) -> None:
+    """The chosen token of each of the first n sequences goes into its slot's ring."""
+    _cuda(hist, "history_append.hist", torch.int32)
+    _cuda(hist_len, "history_append.hist_len", torch.int32)
+    _cuda(chosen, "history_append.chosen", torch.int32)
+    assert seq_slot.numel() >= n and chosen.numel() >= n
+    _check(lib().leb_history_append(_ptr(hist), _ptr(hist_len), _ptr(seq_slot), _ptr(chosen), hist.shape[1], n, _stream()))
 
 
 def argmax(out: torch.Tensor, logits: torch.Tensor) -> None:

@@ -123,6 +123,24 @@ def test_steps_launched_ahead_with_a_window_and_early_stops(dtype, tmp_path):
     eng.cache.check()
 
 
+def test_penalties_on_the_device_match_the_step_by_step_path(dirs):
+    """Repeat and presence penalties in captured decode steps (rings of recent tokens on the device,
+    fed by the steps themselves) against the path that builds every step's history on the host; long
+    enough for the 256-token rings to wrap, prompts longer and shorter than the window."""
+    from lastengine_b200 import Engine, SamplingParams
+    eng = Engine.from_pretrained(dirs["A"], dtype="float32", max_tokens=4096)
+    prompts = H.requests_for(TINY_A, [5, 300, 17], 41)
+    for sp in (SamplingParams(temperature=0.0, repeat_penalty=1.3, presence_penalty=0.4),
+               SamplingParams(temperature=0.8, top_k=30, seed=9, repeat_penalty=1.15)):
+        slow = eng.generate(prompts, sp, max_new_tokens=290, stop_token_ids=[], use_graphs=False)
+        fast = eng.generate(prompts, sp, max_new_tokens=290, stop_token_ids=[])
+        assert fast.tokens == slow.tokens
+        plain = eng.generate(prompts, SamplingParams(temperature=sp.temperature, top_k=sp.top_k, seed=sp.seed),
+                             max_new_tokens=40, stop_token_ids=[])
+        assert plain.tokens[0] != fast.tokens[0][:40]           # the penalties do change what is chosen
+    assert eng.cache.slots.n_held == 0
+
+
 def run_trace(model_dir, dtype, steps, out_dir, max_tokens=1024):
     exe = os.path.join(H.ROOT, "bin", "trace_run")
     p = subprocess.run([sys.executable, exe, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
