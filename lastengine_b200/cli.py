@@ -85,6 +85,38 @@ def cmd_tf_dump(a) -> int:
     return 0
 
 
+def cmd_dense_cmp(a) -> int:
+    """The reference's dense-cmp (src/main.rs:138-158) compares its CPU forward with its GPU forward
+    token by token; here the true 32-bit path stands where the CPU stood and the bfloat16 path is
+    the one under test.  Both follow the 32-bit path's greedy tokens."""
+    import time
+    import torch
+    ids = parse_ids(a.prompt)
+    exact = _engine(a.path, "float32", a.ctx)
+    fast = _engine(a.path, "bfloat16", a.ctx)
+    se, sf = exact.new_sequence(), fast.new_sequence()
+    le = _logprobs(exact.step([se], [ids], "last"))[0].clone()
+    t0 = time.perf_counter()
+    lf = _logprobs(fast.step([sf], [ids], "last"))[0].clone()
+    torch.cuda.synchronize()
+    print(f"bfloat16 prefill {len(ids)} tok in {time.perf_counter() - t0:.3f}s")
+    agree, shown, maxd, sumd = 0, 0, 0.0, 0.0
+    for k in range(a.n):
+        ta, tb = int(torch.argmax(le)), int(torch.argmax(lf))
+        d = abs(float(le[ta]) - float(lf[ta]))
+        maxd, sumd = max(maxd, d), sumd + d
+        if ta == tb:
+            agree += 1
+        elif shown < 8:
+            shown += 1
+            print(f"step {k}: float32 {ta} lp {float(le[ta]):.3f} (bfloat16 lp {float(lf[ta]):.3f}) vs bfloat16 {tb} "
+                  f"lp {float(lf[tb]):.3f} (float32 lp {float(le[tb]):.3f})")
+        le = _logprobs(exact.step([se], [[ta]], "last"))[0].clone()
+        lf = _logprobs(fast.step([sf], [[ta]], "last"))[0].clone()
+    print(f"{agree}/{a.n} argmax agree, mean |dlogprob| {sumd / max(a.n, 1):.4f}, max {maxd:.4f}")
+    return 0
+
+
 def cmd_inspect(a) -> int:
     from .config.base import architecture_name, read_config_json
     from .registry import plan_from_config
@@ -186,6 +218,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("n", nargs="?", type=int, default=100)
     common(p)
     p.set_defaults(fn=cmd_tf_dump)
+
+    p = sub.add_parser("dense-cmp", help="bfloat16 path against the true 32-bit path, greedy step by step")
+    p.add_argument("path")
+    p.add_argument("prompt")
+    p.add_argument("n", nargs="?", type=int, default=32)
+    p.add_argument("--ctx", type=int, default=4096)
+    p.set_defaults(fn=cmd_dense_cmp)
 
     p = sub.add_parser("inspect", help="print the model folder's configuration and tensors")
     p.add_argument("path")

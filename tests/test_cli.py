@@ -63,5 +63,10 @@ def test_generate_gpu_and_tf_dump(tmp_path):
         assert dump["gen_ids"] == rows[0]["tokens"]          # greedy both ways
     p3 = subprocess.run([sys.executable, EXE, "gpu", d, "1,2,3", "3", "--dtype", "float32"], capture_output=True, text=True, timeout=600)
     assert p3.returncode == 0 and p3.stdout.count("logprob") == 3 and "greedy:" in p3.stdout
+    p5 = subprocess.run([sys.executable, EXE, "dense-cmp", d, "1,2,3", "6"], capture_output=True, text=True, timeout=600)
+    assert p5.returncode == 0, p5.stderr[-1500:]
+    last = p5.stdout.splitlines()[-1]
+    assert last.endswith(tuple("0123456789")) and "/6 argmax agree, mean |dlogprob|" in last
+    assert float(last.rsplit("max ", 1)[1]) < 0.05               # bfloat16 against the true 32-bit path
     p4 = subprocess.run([sys.executable, EXE, "probe", "--json"], capture_output=True, text=True, timeout=300)
     assert json.loads(p4.stdout)["gpus"][0]["sm_count"] > 0
