@@ -63,18 +63,29 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
-  pdl_wait();   // the activations come from the kernel before this one
+  pdl_trigger();
+  if (warp == 0 && lane == 0) {
+    // The weights do not depend on the kernel before this one: the weight tiles of the first
+    // stages are asked for before the wait, the activation tiles of those stages after it.
+    const int first = min(my_nk, SK_STAGES);
+    for (int i = 0; i < first; i++) {
+      mbar_expect_tx(&full[i], W_BYTES + X_BYTES);
+      tma_load_2d(sw + i * W_BYTES, &map_w, &full[i], (kb_lo + i) * TC_BK, n0);
+    }
+    pdl_wait();
+    for (int i = 0; i < first; i++) tma_load_2d(sx + i * X_STRIDE, &map_x, &full[i], (kb_lo + i) * TC_BK, 0);
+    for (int i = first; i < my_nk; i++) {
+      const int s = i % SK_STAGES;
+      if (!mbar_wait(&empty[s], ((i / SK_STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 11); break; }
+      mbar_expect_tx(&full[s], W_BYTES + X_BYTES);
+      tma_load_2d(sw + s * W_BYTES, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+      tma_load_2d(sx + s * X_STRIDE, &map_x, &full[s], (kb_lo + i) * TC_BK, 0);
+    }
+  } else {
+    pdl_wait();   // the activations come from the kernel before this one; nothing is written before it
+  }
 
   if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < my_nk; i++) {
-        const int s = i % SK_STAGES;
-        if (!mbar_wait(&empty[s], ((i / SK_STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 11); break; }
-        mbar_expect_tx(&full[s], W_BYTES + X_BYTES);
-        tma_load_2d(sw + s * W_BYTES, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
-        tma_load_2d(sx + s * X_STRIDE, &map_x, &full[s], (kb_lo + i) * TC_BK, 0);
-      }
-    }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
