@@ -17,6 +17,7 @@ holds nothing per sequence but the data itself.
 """
 from __future__ import annotations
 
+import struct
 from dataclasses import dataclass
 
 import numpy as np
@@ -174,6 +175,90 @@ class Cache:
 
     def pages_held(self, slot: int) -> int:
         return max((len(g.seq_pages.get(slot, ())) for g in self.kv_groups), default=0)
+
+    # ---- a sequence as bytes --------------------------------------------------------------
+    def _entry_nbytes(self, entry: int, length: int) -> int:
+        kind, gi = self._where[entry]
+        if kind == "state":
+            g = self.state_groups[gi]
+            return int(np.prod(g.spec.shape, dtype=np.int64)) * g.data.element_size()
+        sp = self.kv_groups[gi].spec
+        return 2 * length * sp.n_kv_heads * sp.head_dim * self.kv_groups[gi].pool.element_size()
+
+    def export_seq(self, slot: int) -> bytes:
+        """What a sequence holds, as bytes: its length (u64, little-endian), then for every cache
+        entry in order its state, or its keys and then its values as `[position][kv head][dim]`
+        in the cache's dtype.  The reference writes one sequence the same way: position count,
+        then per layer the state or K and V up to that position (src/gpu/dense.rs:391-399).
+        Positions that a windowed group has given back are written as zeros."""
+        n = self.length(slot)
+        out = [struct.pack("<Q", n)]
+        raw = lambda t: t.contiguous().view(torch.uint8).cpu().numpy().tobytes()
+        ps = self.page_size
+        for entry in sorted(self._where):
+            kind, gi = self._where[entry]
+            if kind == "state":
+                g = self.state_groups[gi]
+                out.append(raw(g.data[g.index[entry], slot].reshape(-1)))
+                continue
+            g = self.kv_groups[gi]
+            i, sp = g.index[entry], g.spec
+            pages = g.seq_pages.get(slot, [])
+            k = torch.zeros((len(pages) * ps, sp.n_kv_heads, sp.head_dim), dtype=self.dtype, device=self.device)
+            v = torch.zeros_like(k)
+            for j, p in enumerate(pages):
+                if p >= 0:
+                    k[j * ps:(j + 1) * ps] = g.pool[i, 0, p].permute(1, 0, 2)
+                    v[j * ps:(j + 1) * ps] = g.pool[i, 1, p].view(sp.n_kv_heads, sp.head_dim, ps).permute(2, 0, 1)
+            out.append(raw(k[:n].reshape(-1)))
+            out.append(raw(v[:n].reshape(-1)))
+        return b"".join(out)
+
+    def import_seq(self, data: bytes) -> int:
+        """A new sequence that holds what `export_seq` wrote (same model, same dtype).  Raises
+        CacheError when the bytes do not fit this model and CacheFull when there is no room; the
+        cache is then as it was (the reference checks the same two things, src/gpu/dense.rs:400-412)."""
+        if len(data) < 8:
+            raise CacheError("sequence data is too short to hold a length")
+        (n,) = struct.unpack_from("<Q", data, 0)
+        need = 8 + sum(self._entry_nbytes(e, n) for e in self._where)
+        if len(data) != need:
+            raise CacheError(f"sequence data of {len(data)} bytes does not match this model and dtype "
+                             f"({need} bytes for {n} positions)")
+        slot = self.alloc_seq()
+        try:
+            self.reserve({slot: n})
+        except CacheFull:
+            self.free_seq(slot)
+            raise
+        ps, o = self.page_size, 8
+        buf = torch.frombuffer(bytearray(data), dtype=torch.uint8).to(self.device)
+        for entry in sorted(self._where):
+            kind, gi = self._where[entry]
+            nb = self._entry_nbytes(entry, n)
+            if kind == "state":
+                g = self.state_groups[gi]
+                dst = g.data[g.index[entry], slot]
+                dst.copy_(buf[o:o + nb].clone().view(g.data.dtype).view(dst.shape))
+                o += nb
+                continue
+            g = self.kv_groups[gi]
+            i, sp = g.index[entry], g.spec
+            pages = g.seq_pages.get(slot, [])
+            half = nb // 2
+            for which in (0, 1):
+                t = torch.zeros((len(pages) * ps, sp.n_kv_heads, sp.head_dim), dtype=self.dtype, device=self.device)
+                if n:
+                    t[:n] = buf[o:o + half].clone().view(self.dtype).view(n, sp.n_kv_heads, sp.head_dim)
+                o += half
+                for j, p in enumerate(pages):
+                    rows = t[j * ps:(j + 1) * ps]
+                    if which == 0:
+                        g.pool[i, 0, p] = rows.permute(1, 0, 2)
+                    else:
+                        g.pool[i, 1, p].view(sp.n_kv_heads, sp.head_dim, ps).copy_(rows.permute(1, 2, 0))
+        self.commit({slot: n})
+        return slot
 
     # ---- views ---------------------------------------------------------------------------
     def group_of(self, entry: int) -> tuple[str, int] | None:

@@ -99,6 +99,15 @@ class Engine:
     def length(self, seq: int) -> int:
         return self.cache.length(seq)
 
+    def export_sequence(self, seq: int) -> bytes:
+        """The sequence's cache as bytes (`Cache.export_seq`); waits for the device first."""
+        torch.cuda.synchronize(self.device)
+        return self.cache.export_seq(seq)
+
+    def import_sequence(self, data: bytes) -> int:
+        """A new sequence that goes on where the exported one stood."""
+        return self.cache.import_seq(data)
+
     # ---- the step -------------------------------------------------------------------------
     def prepare(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
                 want: str | Sequence[Sequence[int]] | None = "last",

@@ -116,6 +116,50 @@ def test_window_group_gives_pages_back_and_slot_state_is_zeroed():
     assert s2 == s and float(c.state_groups[0].data[:, s2].abs().max()) == 0.0     # reused, and clean
 
 
+def test_a_sequence_goes_out_as_bytes_and_comes_back_in_other_pages():
+    c = make_cache(max_tokens=1280, max_seqs=6)
+    g = torch.Generator().manual_seed(3)
+    for grp in c.kv_groups:
+        grp.pool.copy_(torch.randn(grp.pool.shape, generator=g))
+    other = c.alloc_seq()
+    c.reserve({other: 70}); c.commit({other: 70})          # so that the copy lands in other pages
+    s = c.alloc_seq()
+    for grp in c.state_groups:
+        grp.data[:, s] = torch.randn(grp.data[:, s].shape, generator=g)
+    c.reserve({s: 150}); c.commit({s: 150})
+    data = c.export_seq(s)
+    kv = 2 * 150 * 2 * 16 * 4
+    assert len(data) == 8 + 3 * kv + (16 + 16 + 4) * 4 and int.from_bytes(data[:8], "little") == 150
+    # keys of entry 1 follow the state of entry 0, as [position][kv head][dim]
+    full = c.kv_groups[c.group_of(1)[1]]
+    k = torch.frombuffer(bytearray(data[8 + 64:8 + 64 + kv // 2]), dtype=torch.float32).view(150, 2, 16)
+    assert torch.equal(k[70], full.pool[0, 0, full.seq_pages[s][1], :, 6, :])
+    t = c.import_seq(data)
+    assert t != s and c.length(t) == 150 and c.export_seq(t) == data
+    assert set(full.seq_pages[t]).isdisjoint(full.seq_pages[s])
+    win = c.kv_groups[c.group_of(4)[1]]
+    assert [p >= 0 for p in win.seq_pages[t]] == [p >= 0 for p in win.seq_pages[s]] == [True, True, True]
+    c.check()
+    # bytes of another model, and no room: both leave the cache as it was
+    held, free = c.slots.n_held, [grp.pages.n_free for grp in c.kv_groups]
+    with pytest.raises(CacheError, match="does not match"):
+        c.import_seq(data[:-4])
+    with pytest.raises(CacheError, match="too short"):
+        c.import_seq(b"abc")
+    for _ in range(8):
+        try:
+            c.import_seq(data)
+        except CacheFull:
+            break
+    else:
+        raise AssertionError("the cache never filled")
+    c.check()
+    with pytest.raises(CacheFull):
+        c.import_seq(data)
+    assert c.slots.n_held > held and all(grp.pages.n_free <= f for grp, f in zip(c.kv_groups, free))
+    c.check()
+
+
 def test_xorshift_matches_the_reference_recurrence():
     g = XorShift64(None)
     assert g.state == 0x9E3779B97F4A7C15

@@ -125,6 +125,32 @@ def test_chunked_prompt(dtype, bf16, tol, model_dirs, engines):
     check(torch.cat(out), plain("B", model_dirs, toks, bf16), tol, f"B {dtype} chunked prompt")
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("dtype,bf16,tol", DTYPES)
+def test_sequence_exported_and_imported_goes_on(name, dtype, bf16, tol, model_dirs, engines):
+    """A sequence written out as bytes after 90 tokens, released, and read back into other pages
+    and another slot (a second sequence took its old ones) goes on as if nothing had happened:
+    keys, values (a window's too) and the convolution state all came back."""
+    eng = engines(name, dtype)
+    cfg = CONFIGS[name][0]
+    toks, filler = H.requests_for(cfg, [130, 75], 19)
+    s = eng.new_sequence()
+    out = [eng.step([s], [toks[:90]], [list(range(90))]).float().cpu().clone()]
+    data = eng.export_sequence(s)
+    eng.release(s)
+    f = eng.new_sequence()
+    eng.step([f], [filler], "last")
+    t = eng.import_sequence(data)
+    assert f == s and t != s and eng.length(t) == 90
+    out.append(eng.step([t], [toks[90:100]], [list(range(10))]).float().cpu().clone())
+    for i in range(100, 130):
+        out.append(eng.step([t], [[toks[i]]], [[0]]).float().cpu().clone())
+    eng.release([f, t])
+    check(torch.cat(out), plain(name, model_dirs, toks, bf16), tol, f"{name} {dtype} exported and imported")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
 def test_padding_changes_nothing(model_dirs, engines):
     """Padding sequences (slot -1) in a step leave the real rows' logits bit-identical."""
     eng = engines("A", "float32")
