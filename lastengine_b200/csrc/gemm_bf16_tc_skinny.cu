@@ -17,7 +17,9 @@
 #include "tc_common.cuh"
 
 #define SK_THREADS 192
-#define SK_STAGES 6
+// Stages of the ring.  Up to 64 activation rows a stage has 24 KB and four of them leave room for two
+// blocks per SM: the next product's blocks then start, and fetch their first weights, under this one's.
+#define SK_STAGES_OF(MP) ((MP) > 64 ? 6 : 4)
 
 template <int MP>  // activation rows padded to 16..128 (the MMA's N)
 __global__ void __launch_bounds__(SK_THREADS)
@@ -26,6 +28,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                       int epilogue, int n_slices, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int SK_STAGES = SK_STAGES_OF(MP);
   constexpr int W_BYTES = 128 * TC_BK * 2, X_BYTES = MP * TC_BK * 2;
   uint8_t* sw = smem;
   uint8_t* sx = smem + SK_STAGES * W_BYTES;
@@ -201,6 +204,7 @@ __global__ void skinny_finish_kernel(TC* __restrict__ C, const float* __restrict
 template <int MP>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, float* part, void* C, int c_dtype, int M,
                          int N, int K, int ldc, int epilogue, int n_slices, int* status, cudaStream_t st) {
+  constexpr int SK_STAGES = SK_STAGES_OF(MP);
   constexpr size_t x_stride = ((size_t)MP * TC_BK * 2 + 1023) / 1024 * 1024;
   constexpr size_t smem = SK_STAGES * (128 * TC_BK * 2 + x_stride) + (2 * SK_STAGES + 1) * 8 + 16 + 1024;
   auto kern = gemm_tc_skinny_kernel<MP>;
