@@ -188,6 +188,9 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
 }
 
 // Merge of the splits of one (row, head): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M).
+// A thread owns one dimension and takes the splits eight at a time: maximum, sum and value of all
+// eight are asked for before any is used, so a merge of up to eight splits costs one trip to memory
+// (with more, the running sums are rescaled to the new maximum from group to group).
 template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
                                        const T* __restrict__ gate, int gate_stride, int nh, int hd,
@@ -195,22 +198,37 @@ __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restr
   pdl_wait();
   const size_t m = blockIdx.x;
   const int h = blockIdx.y;
-  const float* pp = part + ((m * nh + h) * n_splits) * (size_t)(hd + 2);
-  float M = ATT_NEG;
-  for (int s = 0; s < n_splits; s++) M = fmaxf(M, pp[(size_t)s * (hd + 2)]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; s++) L += pp[(size_t)s * (hd + 2) + 1] * expf(pp[(size_t)s * (hd + 2)] - M);
-  float g = 1.f;
-  if (gate) {
-    float z = to_f32(gate[m * gate_stride + h]);
-    g = 1.0f / (1.0f + expf(-z));
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  const size_t step = hd + 2;
+  const float* pp = part + ((m * nh + h) * n_splits) * step;
+  const float z = gate ? to_f32(gate[m * gate_stride + h]) : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < n_splits; s++)
-      a += pp[(size_t)s * (hd + 2) + 2 + d] * expf(pp[(size_t)s * (hd + 2)] - M);
-    out[(m * nh + h) * hd + d] = from_f32<T>(a * inv * g);
+    float M = ATT_NEG, L = 0.f, a = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float ms[8], ls[8], as[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        const bool in = s0 + q < n_splits;
+        const float* r = pp + (size_t)(in ? s0 + q : 0) * step;
+        ms[q] = in ? r[0] : ATT_NEG;
+        ls[q] = in ? r[1] : 0.f;
+        as[q] = in ? r[2 + d] : 0.f;
+      }
+      float cm = M;
+#pragma unroll
+      for (int q = 0; q < 8; q++) cm = fmaxf(cm, ms[q]);
+      const float sc = expf(M - cm);   // 0 for the first group (nothing summed yet), 1 when the maximum stays
+      L *= sc;
+      a *= sc;
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        const float e = expf(ms[q] - cm);
+        L += ls[q] * e;
+        a += as[q] * e;
+      }
+      M = cm;
+    }
+    const float g = gate ? 1.0f / (1.0f + expf(-z)) : 1.f;
+    out[(m * nh + h) * hd + d] = from_f32<T>(a * (L > 0.f ? 1.0f / L : 0.f) * g);
   }
 }
 
