@@ -22,8 +22,23 @@
 // quarter-warps of a 16-byte shared load (rows 2i and 2i+1, four pieces each) hit all 32 banks.
 //
 // epilogue: 0 store, 1 add into float C, 2 SwiGLU over interleaved weights (rows 32j..32j+15
-// gate, 32j+16..32j+31 up of the same 16 outputs; C has N/2 columns).
+// gate, 32j+16..32j+31 up of the same 16 outputs; C has N/2 columns), 3 the gated short
+// convolution of a decode step: W is the conv mixer's in_proj [3D, K], a tile takes the rows of
+// B, C and x of 16 channels (three sub-tiles D rows apart), and the epilogue does what the
+// one-token convolution kernel does (shortconv.cu: bx = B*x, taps over the state, y = C*sum,
+// state shifted), so the projection never goes to memory and one launch is saved.
 #include "common.cuh"
+
+// What the convolution epilogue needs beside the product (all null / 0 for the other epilogues).
+struct StreamConv {
+  const float* w;        // [D, Lc] taps, oldest first
+  const float* bias;     // [D] or null
+  float* state;          // [slots, D, Lc-1]
+  const int* row_seq;    // row -> sequence of the step
+  const int* seq_slot;   // sequence -> cache slot (-1: padding)
+  int Lc;
+};
+#define ST_CONV_MAX_LC 5
 
 #define ST_ROWS 16
 #define ST_CHUNK 64
@@ -51,8 +66,10 @@ __device__ __forceinline__ uint4 st_lds(uint32_t addr) {
 template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 __global__ void __launch_bounds__(32 * ST_WARPS)
 gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
-                        int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles) {
+                        int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles, StreamConv cv) {
   constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
+  constexpr bool CONV = NSUB == 3;   // the only user of three sub-tiles
+  const int D3 = N / 3;
   extern __shared__ __align__(128) unsigned char st_smem[];
   pdl_trigger();
   float (*red)[NSUB][ST_ROWS][8 * MT + 1] =
@@ -86,7 +103,9 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
 #pragma unroll
       for (int i = 0; i < ROWS / 4; i++) {
         const int row = i * 4 + (lane >> 3), ch = lane & 7;
-        const int n = min(n0 + row, N - 1), k = k0 + ch * 8;
+        // convolution: sub-tile i/4 is B, C or x (D rows apart) of the tile's 16 channels
+        const int n = CONV ? (i / 4) * D3 + min(p_tile * ST_ROWS + (row & 15), D3 - 1) : min(n0 + row, N - 1);
+        const int k = k0 + ch * 8;
         const bool in = k < K;   // K is a multiple of 8: a piece is inside or outside as a whole
         st_cp16(base + row * 128 + ((ch ^ ((row & 1) << 2)) << 4), W + (size_t)n * K + (in ? k : 0), in ? 16 : 0);
       }
@@ -109,6 +128,26 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
   int q = 0;
   for (int ti = 0; ti < my_tiles; ti++) {
     const int tile = blockIdx.x + ti * gridDim.x;
+    // convolution: thread t owns (row, channel) pairs t, t + threads, ...; their taps and state are
+    // asked for now and used after the product
+    constexpr int CV_PAIRS = CONV ? (ST_ROWS * 8 * MT + 32 * ST_WARPS - 1) / (32 * ST_WARPS) : 1;
+    float cv_w[CV_PAIRS][ST_CONV_MAX_LC], cv_s[CV_PAIRS][ST_CONV_MAX_LC - 1], cv_b[CV_PAIRS];
+    int cv_slot[CV_PAIRS];
+    if constexpr (CONV) {
+#pragma unroll
+      for (int u = 0; u < CV_PAIRS; u++) {
+        const int idx = threadIdx.x + u * 32 * ST_WARPS;
+        const int col = idx / ST_ROWS, chn = tile * ST_ROWS + idx % ST_ROWS;
+        const bool in = idx < ST_ROWS * 8 * MT && col < M && chn < D3;
+        cv_slot[u] = in ? cv.seq_slot[cv.row_seq[col]] : -1;
+        cv_b[u] = (in && cv.bias) ? cv.bias[chn] : 0.f;
+#pragma unroll
+        for (int k = 0; k < ST_CONV_MAX_LC; k++) cv_w[u][k] = (in && k < cv.Lc) ? cv.w[(size_t)chn * cv.Lc + k] : 0.f;
+#pragma unroll
+        for (int k = 0; k < ST_CONV_MAX_LC - 1; k++)
+          cv_s[u][k] = (cv_slot[u] >= 0 && k < cv.Lc - 1) ? cv.state[((size_t)cv_slot[u] * D3 + chn) * (cv.Lc - 1) + k] : 0.f;
+      }
+    }
     float acc[NSUB][MT][4];
 #pragma unroll
     for (int s = 0; s < NSUB; s++)
@@ -150,7 +189,44 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
         red[warp][s][g + 8][t * 8 + 2 * t4 + 1] = acc[s][t][3];
       }
     __syncthreads();
-    if (epilogue == 2) {
+    if constexpr (CONV) {
+      // as shortconv_single_kernel: the projections rounded to bfloat16 as if they had been stored,
+      // taps oldest first, the state shifted by one
+#pragma unroll
+      for (int u = 0; u < CV_PAIRS; u++) {
+        const int idx = threadIdx.x + u * 32 * ST_WARPS;
+        const int col = idx / ST_ROWS, i = idx % ST_ROWS, chn = tile * ST_ROWS + i;
+        if (idx >= ST_ROWS * 8 * MT || col >= M || chn >= D3) continue;
+        float pb = 0.f, pc = 0.f, px = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS; w++) {
+          pb += red[w][0][i][col];
+          pc += red[w][1][i][col];
+          px += red[w][2][i][col];
+        }
+        TC* yo = C + (size_t)col * ldc + chn;
+        if (cv_slot[u] < 0) {   // padding row
+          *yo = from_f32<TC>(0.f);
+          continue;
+        }
+        const float bx = to_f32(from_f32<TC>(pb)) * to_f32(from_f32<TC>(px));
+        float acc = cv_b[u];
+#pragma unroll
+        for (int k = 0; k < ST_CONV_MAX_LC - 1; k++)
+          if (k < cv.Lc - 1) acc += cv_w[u][k] * cv_s[u][k];
+        float wl = 0.f;
+#pragma unroll
+        for (int k = 0; k < ST_CONV_MAX_LC; k++)
+          if (k == cv.Lc - 1) wl = cv_w[u][k];
+        acc += wl * bx;
+        float* sc = cv.state + ((size_t)cv_slot[u] * D3 + chn) * (cv.Lc - 1);
+#pragma unroll
+        for (int k = 0; k < ST_CONV_MAX_LC - 2; k++)
+          if (k < cv.Lc - 2) sc[k] = cv_s[u][k + 1];
+        sc[cv.Lc - 2] = bx;
+        *yo = from_f32<TC>(to_f32(from_f32<TC>(pc)) * acc);
+      }
+    } else if (epilogue == 2) {
       // NSUB == 2: sub-tile 0 holds the gate rows, sub-tile 1 the up rows of outputs 16 * tile + i
       const int jbase = tile * ST_ROWS;
       for (int idx = threadIdx.x; idx < ST_ROWS * 8 * MT; idx += blockDim.x) {
@@ -373,7 +449,7 @@ static int launch_stream_grouped(void* C, const bf16* A, const bf16* W, int P, i
 
 template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, int K, int lda, int ldc,
-                         int epilogue, cudaStream_t st) {
+                         int epilogue, cudaStream_t st, StreamConv cv = StreamConv{}) {
   constexpr int ROWS = ST_ROWS * NSUB;
   constexpr size_t smem = (size_t)ST_WARPS * S * (ROWS + 8 * MT) * 128 + sizeof(float) * ST_WARPS * NSUB * ST_ROWS * (8 * MT + 1);
   static int slots = 0;   // blocks the GPU holds at once
@@ -386,12 +462,12 @@ static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, in
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, 32 * ST_WARPS, smem);
     slots = max(1, per_sm) * max(1, n_sm);
   }
-  const int n_tiles = ceil_div(N, ROWS);
+  const int n_tiles = NSUB == 3 ? ceil_div(N / 3, ST_ROWS) : ceil_div(N, ROWS);
   // the same number of tiles for every block (as far as it goes), all blocks on the GPU at once
   const int per_block = ceil_div(n_tiles, slots);
   const int grid = ceil_div(n_tiles, per_block);
   leb_launch(gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st, (TC*)C, A, W, M, N,
-             K, lda, ldc, epilogue, n_tiles);
+             K, lda, ldc, epilogue, n_tiles, cv);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_stream");
   return 0;
 }
@@ -422,6 +498,23 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
   if (c_dtype == LEB_BF16) return stream_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
   if (c_dtype == LEB_F32) return stream_dispatch<float>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
   return leb_fail("leb_gemm_bf16_stream: unknown C dtype %d", c_dtype);
+}
+
+// The conv mixer's decode step in one launch: y[M, D] = conv(in_proj . h) with the state updated
+// (every row is the one new token of its sequence).  W: in_proj [3D, K]; conv_w [D, Lc]; state
+// [slots, D, Lc-1] float; row_seq / seq_slot as in leb_shortconv.
+LEB_API int leb_gemm_bf16_stream_conv(void* y, const void* A, const void* W, int M, int D, int K, int lda, int ldy,
+                                      const float* conv_w, const float* bias, float* state, const int* row_seq,
+                                      const int* seq_slot, int Lc, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream_conv: %d rows; this kernel takes at most 16", M);
+  LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "leb_gemm_bf16_stream_conv: K (%d) and the row stride of A (%d) must be multiples of 8", K, lda);
+  LEB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "leb_gemm_bf16_stream_conv: A and W must be 16-byte aligned");
+  LEB_REQUIRE(Lc >= 2 && Lc <= ST_CONV_MAX_LC, "leb_gemm_bf16_stream_conv: conv length %d outside 2..%d", Lc, ST_CONV_MAX_LC);
+  LEB_REQUIRE(conv_w && state && row_seq && seq_slot, "leb_gemm_bf16_stream_conv: taps, state and the step's tables are required");
+  StreamConv cv{conv_w, bias, state, row_seq, seq_slot, Lc};
+  if (M <= 8) return launch_stream<bf16, 1, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, cv);
+  return launch_stream<bf16, 2, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, cv);
 }
 
 template <typename TC>

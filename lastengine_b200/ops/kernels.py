@@ -42,6 +42,7 @@ def _declare(L) -> None:
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
         "leb_gemm_bf16_stream_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
+        "leb_gemm_bf16_stream_conv": [P, P, P, I, I, I, I, I, P, P, P, P, P, I, P],
         "leb_gemm_bf16_tc_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gemm_bf16_tc2": [P, I, P, P, I, I, I, I, I, I, P, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
@@ -188,6 +189,33 @@ def shortconv(y: torch.Tensor, bcx: torch.Tensor, w: torch.Tensor, bias: torch.T
     _check(lib().leb_shortconv(_ptr(y), _ptr(bcx), _dt(y, "shortconv"), _ptr(w), _ptr(bias), _ptr(state),
                                _ptr(batch.row_seq), _ptr(batch.seq_slot), _ptr(batch.seq_qstart),
                                None if single else _ptr(batch.seq_qlen), M, batch.n_seqs, D, Lc, _stream()))
+
+
+CONV_FUSED_MAX_LC = 5    # conv lengths the fused decode kernel takes
+
+
+def shortconv_decode_fused(y: torch.Tensor, h: torch.Tensor, w_in: torch.Tensor, w: torch.Tensor,
+                           bias: torch.Tensor | None, state: torch.Tensor, batch, Lc: int) -> bool:
+    """The conv mixer's in_proj and convolution of a decode step in one launch: y = conv(h . w_in^T),
+    state updated.  False (nothing done) when the step is not one of up to SMALL_M sequences with
+    one bfloat16 row each, or the sizes are not the kernel's."""
+    M, D = y.shape
+    K = h.shape[1]
+    if not (h.dtype == torch.bfloat16 and y.dtype == torch.bfloat16 and 0 < M <= SMALL_M
+            and batch.max_qlen == 1 and M == batch.n_seqs and 2 <= Lc <= CONV_FUSED_MAX_LC and K % 8 == 0
+            and h.stride(0) % 8 == 0 and h.stride(1) == 1 and y.stride(1) == 1):
+        return False
+    _cuda(h, "shortconv.h", contiguous=False)
+    _cuda(w_in, "shortconv.w_in", torch.bfloat16)
+    _cuda(w, "shortconv.w", torch.float32)
+    _cuda(state, "shortconv.state", torch.float32)
+    assert w_in.shape == (3 * D, K) and w.numel() == D * Lc and state.shape[1:] == (D, Lc - 1)
+    if bias is not None:
+        _cuda(bias, "shortconv.bias", torch.float32)
+    _check(lib().leb_gemm_bf16_stream_conv(_ptr(y), _ptr(h), _ptr(w_in), M, D, K, h.stride(0), y.stride(0), _ptr(w),
+                                           _ptr(bias), _ptr(state), _ptr(batch.row_seq), _ptr(batch.seq_slot), Lc,
+                                           _stream()))
+    return True
 
 
 def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | None,

@@ -38,8 +38,10 @@ class ShortConvMixer(Mixer):
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         M = h.shape[0]
         ws = env.workspace
-        bcx = ws.get("conv.bcx", (M, 3 * self.D), env.dtype)
-        kernels.linear(bcx, h, self.w_in)
         y = ws.get("conv.y", (M, self.D), env.dtype)
-        kernels.shortconv(y, bcx, self.w_conv, None, cache.state, batch, self.Lc)
+        # a decode step of a few sequences: projection and convolution in one launch
+        if not kernels.shortconv_decode_fused(y, h, self.w_in, self.w_conv, None, cache.state, batch, self.Lc):
+            bcx = ws.get("conv.bcx", (M, 3 * self.D), env.dtype)
+            kernels.linear(bcx, h, self.w_in)
+            kernels.shortconv(y, bcx, self.w_conv, None, cache.state, batch, self.Lc)
         kernels.linear(out, y, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)

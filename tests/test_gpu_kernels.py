@@ -313,6 +313,52 @@ def test_shortconv_many_rows(Lc, D):
         assert err(state[slots[i]].cpu().T, padded[-(Lc - 1):]) < 1e-6, i
 
 
+@pytest.mark.parametrize("B,D,K_,Lc", [(8, 2048, 2048, 3), (1, 72, 40, 2), (13, 136, 200, 4), (16, 48, 64, 5), (5, 100, 72, 3)])
+def test_shortconv_decode_fused(B, D, K_, Lc):
+    """Projection and convolution of a decode step in one launch, three steps in a row so that the
+    state it writes is the state it reads next; one sequence is padding, the slots are not in order
+    and other slots hold stale values.  Compared with the plain formulas (projection rounded to
+    bfloat16 as the two-kernel path stores it) and with the two-kernel path itself."""
+    h_all = [gen(B, K_, seed=60 + t, dtype=torch.bfloat16) for t in range(3)]
+    w_in = gen(3 * D, K_, seed=63, scale=0.05, dtype=torch.bfloat16)
+    w = gen(D, Lc, seed=64)
+    slots = [(5 * i + 3) % (B + 3) for i in range(B)]
+    if B > 2:
+        slots[1] = -1
+    state = torch.full((B + 3, D, Lc - 1), 7.0, device=DEV)
+    start = gen(B, D, Lc - 1, seed=65)
+    for i, s in enumerate(slots):
+        if s >= 0:
+            state[s] = start[i].to(DEV)
+    state2 = state.clone()
+    hist = start.double().permute(0, 2, 1).clone()          # [B, Lc-1, D], oldest first
+    bb = builder()
+    for t in range(3):
+        batch = bb.build(slots, [[0]] * B, [t] * B, [], {})
+        y = torch.full((B, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+        assert K().shortconv_decode_fused(y, h_all[t].to(DEV), w_in.to(DEV), w.to(DEV), None, state, batch, Lc)
+        bcx = torch.empty(B, 3 * D, device=DEV, dtype=torch.bfloat16)
+        K().linear(bcx, h_all[t].to(DEV), w_in.to(DEV))
+        y2 = torch.empty(B, D, device=DEV, dtype=torch.bfloat16)
+        K().shortconv(y2, bcx, w.to(DEV), None, state2, batch, Lc)
+        p = (h_all[t].double() @ w_in.double().T).to(torch.bfloat16).double()
+        bx = p[:, :D] * p[:, 2 * D:]
+        taps = torch.cat([hist, bx[:, None]], dim=1)          # [B, Lc, D]
+        want = p[:, D:2 * D] * (taps * w.double().T[None]).sum(1)
+        hist = taps[:, 1:]
+        for i, s in enumerate(slots):
+            if s < 0:
+                assert float(y[i].abs().max()) == 0.0
+                continue
+            assert err(y[i], want[i]) < 6e-3, (t, i)
+            assert err(y[i], y2[i].float().cpu()) < 6e-3, (t, i)
+            assert err(state[s].cpu().T, hist[i]) < 6e-3, (t, i)
+    used = [s for s in slots if s >= 0]
+    for s in range(B + 3):
+        if s not in used:
+            assert float(state[s].min()) == 7.0 and float(state[s].max()) == 7.0
+
+
 # ---- rotation and cache write ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rope_dim,lens", [(4, 2, 16, 16, [3, 70]), (3, 1, 48, 32, [3, 70]), (5, 5, 80, 80, [3, 70]),
