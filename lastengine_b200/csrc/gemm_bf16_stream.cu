@@ -40,6 +40,23 @@ struct StreamConv {
 };
 #define ST_CONV_MAX_LC 5
 
+// An RMSNorm split between the product before it and the product after it (decode steps, where a
+// norm kernel of its own costs more in launch latency than in work).  The product that adds into
+// the residual x also leaves bf16(x * g) (g: the norm's weight) and, per row and tile of 16
+// columns, the sum of x^2; the product that follows reads the former as its activations, adds the
+// latter up and multiplies its float sums by rsqrt(sum / D + eps).  Sum of squares, root and the
+// scaling are float; the scale is applied after the product instead of before the rounding to
+// bfloat16, which leaves the same relative rounding error.
+struct StreamNorm {
+  const float* ssq_in;   // [rows, parts_in] partial sums of squares of this product's input rows, or null
+  int parts_in;
+  int d_in;              // width of the input rows (what the mean is taken over)
+  float eps;
+  bf16* emit_vals;       // [rows, N] bf16(x_new * emit_g), or null (epilogue 1 only)
+  const float* emit_g;   // [N]
+  float* emit_ssq;       // [rows, ceil(N / 16)]
+};
+
 #define ST_ROWS 16
 #define ST_CHUNK 64
 
@@ -66,7 +83,7 @@ __device__ __forceinline__ uint4 st_lds(uint32_t addr) {
 template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 __global__ void __launch_bounds__(32 * ST_WARPS)
 gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
-                        int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles, StreamConv cv) {
+                        int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles, StreamConv cv, StreamNorm nm) {
   constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
   constexpr bool CONV = NSUB == 3;   // the only user of three sub-tiles
   const int D3 = N / 3;
@@ -125,6 +142,23 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
   for (int i = 0; i < S - 1; i++)
     if (i < total) issue_x(i, i % my_chunks);
   st_commit();
+  // split norm: warp w adds up the partial sums of squares of rows w, w + warps, ...; the loads go
+  // out now and are used after the first tile's product
+  constexpr int NR = (8 * MT + ST_WARPS - 1) / ST_WARPS;   // rows a warp looks after
+  constexpr int NP = 8;                                    // partial sums a lane holds per row (more: a loop)
+  __shared__ float row_scale[8 * MT];
+  float ssq_part[NR][NP];
+  if (nm.ssq_in) {
+#pragma unroll
+    for (int a = 0; a < NR; a++) {
+      const int row = warp + a * ST_WARPS;
+#pragma unroll
+      for (int b = 0; b < NP; b++) {
+        const int part = lane + 32 * b;
+        ssq_part[a][b] = (row < M && part < nm.parts_in) ? nm.ssq_in[(size_t)row * nm.parts_in + part] : 0.f;
+      }
+    }
+  }
   int q = 0;
   for (int ti = 0; ti < my_tiles; ti++) {
     const int tile = blockIdx.x + ti * gridDim.x;
@@ -188,6 +222,22 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
         red[warp][s][g + 8][t * 8 + 2 * t4] = acc[s][t][2];
         red[warp][s][g + 8][t * 8 + 2 * t4 + 1] = acc[s][t][3];
       }
+    if (ti == 0) {
+#pragma unroll
+      for (int a = 0; a < NR; a++) {
+        const int row = warp + a * ST_WARPS;
+        float sum = 0.f;
+        if (nm.ssq_in) {
+#pragma unroll
+          for (int b = 0; b < NP; b++) sum += ssq_part[a][b];
+          for (int part = lane + 32 * NP; part < nm.parts_in; part += 32)   // wider rows than 32 * NP tiles
+            if (row < M) sum += nm.ssq_in[(size_t)row * nm.parts_in + part];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (lane == 0 && row < 8 * MT) row_scale[row] = nm.ssq_in ? 1.0f / sqrtf(sum / (float)nm.d_in + nm.eps) : 1.f;
+      }
+    }
     __syncthreads();
     if constexpr (CONV) {
       // as shortconv_single_kernel: the projections rounded to bfloat16 as if they had been stored,
@@ -204,6 +254,9 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
           pc += red[w][1][i][col];
           px += red[w][2][i][col];
         }
+        pb *= row_scale[col];
+        pc *= row_scale[col];
+        px *= row_scale[col];
         TC* yo = C + (size_t)col * ldc + chn;
         if (cv_slot[u] < 0) {   // padding row
           *yo = from_f32<TC>(0.f);
@@ -238,20 +291,34 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
           gt += red[w][0][i][col];
           up += red[w][NSUB - 1][i][col];
         }
+        gt *= row_scale[col];
+        up *= row_scale[col];
         C[(size_t)col * ldc + jbase + i] = from_f32<TC>(gt / (1.0f + expf(-gt)) * up);
       }
     } else {
       const int n0 = tile * ROWS;
+      // ROWS * 8 * MT is a multiple of the block's threads or smaller than them, and ROWS a multiple
+      // of 16: the 16 lanes of a half-warp hold 16 consecutive columns of one row, all or none
       for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {
         const int col = idx / ROWS, rr = idx % ROWS;
         const int n = n0 + rr;
-        if (col >= M || n >= N) continue;
+        const bool in = col < M && n < N;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < ST_WARPS; w++) v += red[w][rr / ST_ROWS][rr % ST_ROWS][col];
+        v *= row_scale[col];
         TC* cp = C + (size_t)col * ldc + n;
-        if (epilogue == 1) v += to_f32(*cp);
-        *cp = from_f32<TC>(v);
+        if (in) {
+          if (epilogue == 1) v += to_f32(*cp);
+          *cp = from_f32<TC>(v);
+        }
+        if (nm.emit_vals) {   // epilogue 1: the new residual, for the norm that follows
+          float sq = in ? v * v : 0.f;
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          if (in) nm.emit_vals[(size_t)col * N + n] = __float2bfloat16_rn(v * nm.emit_g[n]);
+          if ((rr & 15) == 0 && col < M && n < N) nm.emit_ssq[(size_t)col * ((N + 15) / 16) + n / 16] = sq;
+        }
       }
     }
     __syncthreads();   // the sums are read before the next tile's are written
@@ -449,7 +516,7 @@ static int launch_stream_grouped(void* C, const bf16* A, const bf16* W, int P, i
 
 template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, int K, int lda, int ldc,
-                         int epilogue, cudaStream_t st, StreamConv cv = StreamConv{}) {
+                         int epilogue, cudaStream_t st, StreamNorm nm, StreamConv cv = StreamConv{}) {
   constexpr int ROWS = ST_ROWS * NSUB;
   constexpr size_t smem = (size_t)ST_WARPS * S * (ROWS + 8 * MT) * 128 + sizeof(float) * ST_WARPS * NSUB * ST_ROWS * (8 * MT + 1);
   static int slots = 0;   // blocks the GPU holds at once
@@ -467,26 +534,30 @@ static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, in
   const int per_block = ceil_div(n_tiles, slots);
   const int grid = ceil_div(n_tiles, per_block);
   leb_launch(gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st, (TC*)C, A, W, M, N,
-             K, lda, ldc, epilogue, n_tiles, cv);
+             K, lda, ldc, epilogue, n_tiles, cv, nm);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_stream");
   return 0;
 }
 
 template <typename TC>
 static int stream_dispatch(void* C, const bf16* a, const bf16* w, int M, int N, int K, int lda, int ldc, int epilogue,
-                           cudaStream_t st) {
+                           cudaStream_t st, StreamNorm nm) {
   if (epilogue == 2) {
-    if (M <= 8) return launch_stream<TC, 1, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st);
-    return launch_stream<TC, 2, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+    if (M <= 8) return launch_stream<TC, 1, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
+    return launch_stream<TC, 2, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
   }
   // few tiles (at most one per SM) and a long K: deeper rings instead of a second block per SM
-  if (M <= 8 && ceil_div(N, ST_ROWS) <= 148 && K >= 4096) return launch_stream<TC, 1, 1, 8, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st);
-  if (M <= 8) return launch_stream<TC, 1, 1, 4, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st);
-  return launch_stream<TC, 2, 1, 3, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st);
+  if (M <= 8 && ceil_div(N, ST_ROWS) <= 148 && K >= 4096) return launch_stream<TC, 1, 1, 8, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
+  if (M <= 8) return launch_stream<TC, 1, 1, 4, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
+  return launch_stream<TC, 2, 1, 3, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
 }
 
+// Split norm (see StreamNorm), both optional: `ssq_in` [M, parts_in] with `d_in` and `eps` scales the
+// product's rows by rsqrt(sum / d_in + eps); `emit_vals` [M, N], `emit_g` [N], `emit_ssq`
+// [M, ceil(N/16)] make an adding product leave what the next norm needs.
 LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
-                                 int ldc, int epilogue, cudaStream_t st) {
+                                 int ldc, int epilogue, const float* ssq_in, int parts_in, int d_in, float eps,
+                                 void* emit_vals, const float* emit_g, float* emit_ssq, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream: %d rows; this kernel takes at most 16", M);
   LEB_REQUIRE(K > 0 && K % 8 == 0, "leb_gemm_bf16_stream: K (%d) must be a multiple of 8", K);
@@ -495,8 +566,11 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
   LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_stream: unknown epilogue %d", epilogue);
   LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_stream: adding needs a float C");
   LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_stream: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
-  if (c_dtype == LEB_BF16) return stream_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
-  if (c_dtype == LEB_F32) return stream_dispatch<float>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st);
+  LEB_REQUIRE(!emit_vals || (epilogue == 1 && emit_g && emit_ssq), "leb_gemm_bf16_stream: only an adding product leaves the next norm's input, and it needs the weight and the sums' place");
+  LEB_REQUIRE(!ssq_in || (parts_in > 0 && d_in > 0), "leb_gemm_bf16_stream: the sums of squares need their count and the row width");
+  StreamNorm nm{ssq_in, parts_in, d_in, eps, (bf16*)emit_vals, emit_g, emit_ssq};
+  if (c_dtype == LEB_BF16) return stream_dispatch<bf16>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st, nm);
+  if (c_dtype == LEB_F32) return stream_dispatch<float>(C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldc, epilogue, st, nm);
   return leb_fail("leb_gemm_bf16_stream: unknown C dtype %d", c_dtype);
 }
 
@@ -505,16 +579,19 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
 // [slots, D, Lc-1] float; row_seq / seq_slot as in leb_shortconv.
 LEB_API int leb_gemm_bf16_stream_conv(void* y, const void* A, const void* W, int M, int D, int K, int lda, int ldy,
                                       const float* conv_w, const float* bias, float* state, const int* row_seq,
-                                      const int* seq_slot, int Lc, cudaStream_t st) {
+                                      const int* seq_slot, int Lc, const float* ssq_in, int parts_in, int d_in,
+                                      float eps, cudaStream_t st) {
   if (M <= 0 || D <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream_conv: %d rows; this kernel takes at most 16", M);
   LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "leb_gemm_bf16_stream_conv: K (%d) and the row stride of A (%d) must be multiples of 8", K, lda);
   LEB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "leb_gemm_bf16_stream_conv: A and W must be 16-byte aligned");
   LEB_REQUIRE(Lc >= 2 && Lc <= ST_CONV_MAX_LC, "leb_gemm_bf16_stream_conv: conv length %d outside 2..%d", Lc, ST_CONV_MAX_LC);
   LEB_REQUIRE(conv_w && state && row_seq && seq_slot, "leb_gemm_bf16_stream_conv: taps, state and the step's tables are required");
+  LEB_REQUIRE(!ssq_in || (parts_in > 0 && d_in > 0), "leb_gemm_bf16_stream_conv: the sums of squares need their count and the row width");
   StreamConv cv{conv_w, bias, state, row_seq, seq_slot, Lc};
-  if (M <= 8) return launch_stream<bf16, 1, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, cv);
-  return launch_stream<bf16, 2, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, cv);
+  StreamNorm nm{ssq_in, parts_in, d_in, eps, nullptr, nullptr, nullptr};
+  if (M <= 8) return launch_stream<bf16, 1, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
+  return launch_stream<bf16, 2, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
 }
 
 template <typename TC>

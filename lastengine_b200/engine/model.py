@@ -72,10 +72,20 @@ class Model:
         M, D = batch.n_rows, self.hidden_size
         x = ws.get("model.x", (M, D), torch.float32)
         self.embedding.forward(x, batch.tokens)
-        for i, e in enumerate(self.plan.schedule):
+        sched = self.plan.schedule
+        pending = None      # the half of the next block's first norm that the last block left (decode steps)
+        for i, e in enumerate(sched):
             entry = i if e.cache is None else e.cache
             view = cache.view(entry, e.writes_cache and entry == i, batch.tables)
-            self.blocks[e.layer].forward(x, batch, view, env)
+            block = self.blocks[e.layer]
+            after = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+            # (norm, part that reads it) of the block that runs next, for blocks that can split a norm
+            env.next_block_norm = after.first_reader() if hasattr(after, "first_reader") else None
+            if pending is not None:
+                pending = block.forward(x, batch, view, env, pending=pending)
+            else:
+                pending = block.forward(x, batch, view, env)
+        env.next_block_norm = None
         R = batch.n_logit_rows
         logits = ws.get("model.logits", (R, self.vocab_size), torch.float32)
         if R:

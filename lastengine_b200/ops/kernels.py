@@ -40,9 +40,9 @@ def _declare(L) -> None:
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
-        "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P],
+        "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P, I, I, F, P, P, P, P],
         "leb_gemm_bf16_stream_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
-        "leb_gemm_bf16_stream_conv": [P, P, P, I, I, I, I, I, P, P, P, P, P, I, P],
+        "leb_gemm_bf16_stream_conv": [P, P, P, I, I, I, I, I, P, P, P, P, P, I, P, I, I, F, P],
         "leb_gemm_bf16_tc_grouped": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
         "leb_gemm_bf16_tc2": [P, I, P, P, I, I, I, I, I, I, P, P],
         "leb_moe_router": [P, P, P, I, P, P, I, I, I, I, I, F, P],
@@ -195,7 +195,8 @@ CONV_FUSED_MAX_LC = 5    # conv lengths the fused decode kernel takes
 
 
 def shortconv_decode_fused(y: torch.Tensor, h: torch.Tensor, w_in: torch.Tensor, w: torch.Tensor,
-                           bias: torch.Tensor | None, state: torch.Tensor, batch, Lc: int) -> bool:
+                           bias: torch.Tensor | None, state: torch.Tensor, batch, Lc: int,
+                           scale: "SplitNorm | None" = None) -> bool:
     """The conv mixer's in_proj and convolution of a decode step in one launch: y = conv(h . w_in^T),
     state updated.  False (nothing done) when the step is not one of up to SMALL_M sequences with
     one bfloat16 row each, or the sizes are not the kernel's."""
@@ -212,9 +213,10 @@ def shortconv_decode_fused(y: torch.Tensor, h: torch.Tensor, w_in: torch.Tensor,
     assert w_in.shape == (3 * D, K) and w.numel() == D * Lc and state.shape[1:] == (D, Lc - 1)
     if bias is not None:
         _cuda(bias, "shortconv.bias", torch.float32)
+    ssq, parts, d_in, eps = _scale_args(scale, M, K)
     _check(lib().leb_gemm_bf16_stream_conv(_ptr(y), _ptr(h), _ptr(w_in), M, D, K, h.stride(0), y.stride(0), _ptr(w),
                                            _ptr(bias), _ptr(state), _ptr(batch.row_seq), _ptr(batch.seq_slot), Lc,
-                                           _stream()))
+                                           ssq, parts, d_in, eps, _stream()))
     return True
 
 
@@ -355,8 +357,34 @@ SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcg
 # the next product starts up and fetches its first weights.  So the norm stays a kernel of its own.
 
 
+class SplitNorm:
+    """An RMSNorm split between the product before it and the product after it (decode steps).
+
+    `values` [M, D] is bfloat16(x * weight) and `ssq` [M, ceil(D/16)] holds partial sums of x^2,
+    both left by the product that added into the residual x (`linear(..., emit=...)`); the product
+    that takes `values` as its input multiplies its float sums by rsqrt(sum(ssq) / D + eps)
+    (`linear(..., scale=...)`).  Only the weight-streaming product of up to SMALL_M rows does
+    either; `split_norm_ok` says whether a step qualifies."""
+
+    def __init__(self, values: torch.Tensor, ssq: torch.Tensor, weight: torch.Tensor, eps: float):
+        self.values, self.ssq, self.weight, self.eps = values, ssq, weight, float(eps)
+        self.filled = False      # set by the product that wrote values and ssq
+
+
+def split_norm_ok(M: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and 0 < M <= SMALL_M
+
+
+def _scale_args(scale: "SplitNorm | None", M: int, K: int):
+    if scale is None:
+        return None, 0, 0, 0.0
+    assert scale.filled and scale.values.shape == (M, K) and scale.ssq.shape[0] >= M
+    return _ptr(scale.ssq), scale.ssq.shape[1], K, scale.eps
+
+
 def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
-           group_offsets: torch.Tensor | None = None, rows_hint: int = 0, streaming: bool = False) -> None:
+           group_offsets: torch.Tensor | None = None, rows_hint: int = 0, streaming: bool = False,
+           scale: SplitNorm | None = None, emit: SplitNorm | None = None) -> None:
     """out (+)= x . w^T  with w [N, K] (or [E, N, K] with group_offsets [E+1] over the rows).
 
     float32 operands run on the CUDA cores in true 32-bit; bfloat16 operands on the tensor
@@ -400,9 +428,18 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
     tc = _OPTIONAL_TC[0]
     if not streaming and group_offsets is None and M <= SMALL_M:
         # the decode step: W streamed through rings of asynchronous copies in shared memory
+        ssq, parts, d_in, eps = _scale_args(scale, M, K)
+        ev = eg = es = None
+        if emit is not None:
+            assert epilogue == ACCUMULATE and emit.values.shape == (M, N) and emit.ssq.shape == (M, -(-N // 16))
+            assert emit.values.is_contiguous() and emit.ssq.is_contiguous() and emit.weight.numel() == N
+            ev, eg, es = _ptr(emit.values), _ptr(emit.weight), _ptr(emit.ssq)
+            emit.filled = True
         _check(L.leb_gemm_bf16_stream(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
-                                      epilogue, _stream()))
+                                      epilogue, ssq, parts, d_in, eps, ev, eg, es, _stream()))
         return
+    if scale is not None:
+        raise KernelError("linear: a split norm goes with the weight-streaming product of a decode step only")
     # few dozen rows: W as the wide operand with K sliced over blocks, unless N alone already gives
     # every SM several tiles (the output head), where the persistent kernel streams W better
     if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296

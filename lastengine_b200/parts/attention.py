@@ -20,6 +20,8 @@ from .base import MATRIX, NORM, BuildEnv, KVSpec, Mixer, PartSpec, TensorSpec
 
 @MIXERS.register("attention")
 class AttentionMixer(Mixer):
+    split_norm = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  norm_eps: float, qk_norm: bool = True, position: PartSpec | None = None,
                  window: int = 0, output_gate: bool = False, own_kv: bool = True,
@@ -74,6 +76,7 @@ class AttentionMixer(Mixer):
         nh, nkv, hd = self.nh, self.nkv, self.hd
         M = h.shape[0]
         ws = env.workspace
+        scale, emit = env.take_split_in(), env.take_split_out()
         writes = self.own_kv and cache.writable
         if self.own_kv and not cache.writable:
             w_in = self.w_in[: nh * hd] if not self.output_gate else None
@@ -82,7 +85,7 @@ class AttentionMixer(Mixer):
         if w_in is None:  # q and gate rows are not adjacent once k, v are skipped: two products
             raise NotImplementedError("a gated attention layer reading another layer's cache")
         proj = ws.get("attn.proj", (M, w_in.shape[0]), env.dtype)
-        kernels.linear(proj, h, w_in)
+        kernels.linear(proj, h, w_in, scale=scale)
         q_in = proj[:, : nh * hd]
         k_in = v_in = gate = None
         col = nh * hd
@@ -104,4 +107,5 @@ class AttentionMixer(Mixer):
             scratch = ws.get("attn.part", (M * nh * n_splits * (hd + 2),), torch.float32)
         kernels.attention(o, q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd, cache.page_size,
                           self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch)
-        kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)
+        kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE,
+                       emit=emit if accumulate else None)

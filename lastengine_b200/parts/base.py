@@ -131,6 +131,21 @@ class BuildEnv:
     device: torch.device
     dtype: torch.dtype                 # activation / matrix dtype: float32 or bfloat16
     workspace: Any = None              # engine.workspace.Workspace
+    # A norm split between two products (ops.kernels.SplitNorm), handed from a block to a part for
+    # one call.  A part that sets `split_norm = True` takes `split_in` (its input rows are then
+    # the split's values, and its first product scales by the split) and `split_out` (its last
+    # adding product leaves the split's values and sums); the others never look at them.
+    split_in: Any = None
+    split_out: Any = None
+    next_block_norm: Any = None        # the norm that reads the residual after this block (set by the model)
+
+    def take_split_in(self):
+        s, self.split_in = self.split_in, None
+        return s
+
+    def take_split_out(self):
+        s, self.split_out = self.split_out, None
+        return s
 
     @property
     def is_float32(self) -> bool:
@@ -138,6 +153,8 @@ class BuildEnv:
 
 
 class Part:
+    split_norm = False     # True: forward() honours env.split_in / env.split_out (see BuildEnv)
+
     def tensors(self) -> dict[str, TensorSpec]:
         return {}
 

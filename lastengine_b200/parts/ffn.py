@@ -33,6 +33,8 @@ def fuse_gate_up(w1: torch.Tensor, w3: torch.Tensor, interleave: bool) -> torch.
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    split_norm = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.D, self.F = int(hidden_size), int(intermediate_size)
         self.w13 = self.w2 = None
@@ -51,14 +53,16 @@ class SwiGLU(FeedForward):
     def forward(self, h, out, accumulate, batch, env) -> None:
         M = h.shape[0]
         ws = env.workspace
+        scale, emit = env.take_split_in(), env.take_split_out()
         a = ws.get("ffn.a", (M, self.F), env.dtype)
         if self.fused:
-            kernels.linear(a, h, self.w13, kernels.SWIGLU)
+            kernels.linear(a, h, self.w13, kernels.SWIGLU, scale=scale)
         else:
             gu = ws.get("ffn.gu", (M, 2 * self.F), torch.float32)
-            kernels.linear(gu, h, self.w13)
+            kernels.linear(gu, h, self.w13, scale=scale)
             kernels.swiglu(a, gu)
-        kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE)
+        kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE,
+                       emit=emit if accumulate else None)
 
 
 @FEED_FORWARDS.register("sigmoid_topk_moe")

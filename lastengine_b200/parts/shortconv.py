@@ -15,6 +15,8 @@ from .base import MATRIX, VECTOR, BuildEnv, Mixer, StateSpec, TensorSpec
 
 @MIXERS.register("shortconv")
 class ShortConvMixer(Mixer):
+    split_norm = True
+
     def __init__(self, hidden_size: int, L_cache: int):
         if not 2 <= L_cache <= 17:
             raise ValueError(f"conv_L_cache {L_cache} outside what the kernel takes (2..17)")
@@ -38,10 +40,12 @@ class ShortConvMixer(Mixer):
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         M = h.shape[0]
         ws = env.workspace
+        scale, emit = env.take_split_in(), env.take_split_out()
         y = ws.get("conv.y", (M, self.D), env.dtype)
         # a decode step of a few sequences: projection and convolution in one launch
-        if not kernels.shortconv_decode_fused(y, h, self.w_in, self.w_conv, None, cache.state, batch, self.Lc):
+        if not kernels.shortconv_decode_fused(y, h, self.w_in, self.w_conv, None, cache.state, batch, self.Lc, scale=scale):
             bcx = ws.get("conv.bcx", (M, 3 * self.D), env.dtype)
-            kernels.linear(bcx, h, self.w_in)
+            kernels.linear(bcx, h, self.w_in, scale=scale)
             kernels.shortconv(y, bcx, self.w_conv, None, cache.state, batch, self.Lc)
-        kernels.linear(out, y, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE)
+        kernels.linear(out, y, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE,
+                       emit=emit if accumulate else None)

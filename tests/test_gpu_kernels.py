@@ -359,6 +359,35 @@ def test_shortconv_decode_fused(B, D, K_, Lc):
             assert float(state[s].min()) == 7.0 and float(state[s].max()) == 7.0
 
 
+@pytest.mark.parametrize("M,D,K_,N2", [(8, 2048, 2048, 6144), (1, 72, 40, 64), (13, 136, 200, 96), (16, 104, 64, 32)])
+def test_norm_split_between_two_products(M, D, K_, N2):
+    """An RMSNorm split between the product that adds into the residual and the product that reads
+    the normed rows (decode steps): the first leaves bfloat16(x * g) and partial sums of x^2, the
+    second scales its sums by rsqrt(mean + eps).  Compared with norm and products in float64."""
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    eps = 3e-5
+    a, w = gen(M, K_, seed=70, dtype=torch.bfloat16), gen(D, K_, seed=71, scale=0.05, dtype=torch.bfloat16)
+    x0, g = gen(M, D, seed=72, scale=3.0), 1.0 + gen(D, seed=73, scale=0.3)
+    x = x0.to(DEV)
+    sp = K().SplitNorm(torch.empty(M, D, device=DEV, dtype=torch.bfloat16),
+                       torch.full((M, -(-D // 16)), float("nan"), device=DEV), g.to(DEV), eps)
+    K().linear(x, a.to(DEV), w.to(DEV), K().ACCUMULATE, emit=sp)
+    assert sp.filled
+    xn = x0.double() + a.double() @ w.double().T
+    assert err(x, xn) < 2e-5
+    assert err(sp.values, xn * g.double()) < 5e-3
+    assert err(sp.ssq.sum(1), (xn ** 2).sum(1)) < 1e-5
+    normed = xn * torch.rsqrt((xn ** 2).mean(1, keepdim=True) + eps) * g.double()
+    w2 = gen(N2, D, seed=74, scale=0.05, dtype=torch.bfloat16)
+    out = torch.empty(M, N2, device=DEV, dtype=torch.bfloat16)
+    K().linear(out, sp.values, w2.to(DEV), scale=sp)
+    assert err(out, normed @ w2.double().T) < 6e-3
+    F = N2 // 2
+    o2 = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    K().linear(o2, sp.values, fuse_gate_up(w2[:F], w2[F:], True).to(DEV), K().SWIGLU, scale=sp)
+    assert err(o2, P.silu(normed @ w2[:F].double().T) * (normed @ w2[F:].double().T)) < 6e-3
+
+
 # ---- rotation and cache write ---------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rope_dim,lens", [(4, 2, 16, 16, [3, 70]), (3, 1, 48, 32, [3, 70]), (5, 5, 80, 80, [3, 70]),
