@@ -48,6 +48,7 @@ __device__ __forceinline__ uint4 atd_lds(uint32_t addr) {
 // stages of a warp's ring (8 KB each at head size 64).  Two are enough to keep a block in flight
 // while one is multiplied, and leave room for three blocks per SM: the loop is a chain of
 // dependent tensor-core and exponential steps, and more warps hide it better than deeper rings.
+// A launch of so few blocks that an SM gets two at most takes three stages instead.
 #define ATD_STAGES(HD) ((HD) <= 32 ? 3 : 2)
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -67,7 +68,7 @@ __device__ __forceinline__ uint4 mask_positions(uint4 v, int first, int lo, int 
   return v;
 }
 
-template <int HD>  // head_dim, a multiple of 32
+template <int HD, int S>  // head_dim, a multiple of 32; stages of a warp's ring
 __global__ void __launch_bounds__(32 * ATD_WARPS)
 attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const bf16* __restrict__ q,
                         const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
@@ -78,7 +79,6 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
                         int n_splits) {
   constexpr int KB = HD / 32;  // 32-wide pieces of head_dim
   constexpr int NT = HD / 8;   // 8-wide output tiles over head_dim
-  constexpr int S = ATD_STAGES(HD);
   constexpr int KBYTES = 32 * HD * 2, STAGE = 2 * KBYTES;   // keys, then values
   // head sizes whose key rows are a multiple of 128 bytes: the pieces of odd rows are moved by 4
   // places so that the two rows a quarter-warp reads fall on different banks
@@ -327,25 +327,32 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
   LEB_REQUIRE(n_splits >= 1 && (n_splits == 1 || part), "leb_attention_decode: splits need scratch");
   dim3 grid(nkv, B, n_splits);
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention_decode: grid too large");
-#define LEB_ATD(HD_)                                                                              \
+#define LEB_ATD(HD_, S_)                                                                          \
   {                                                                                               \
-    constexpr int smem = ATD_WARPS * ATD_STAGES(HD_) * 2 * 32 * HD_ * 2;                           \
+    constexpr int smem = ATD_WARPS * S_ * 2 * 32 * HD_ * 2;                                        \
     static bool set = false;                                                                      \
     if (!set) {                                                                                   \
-      if (cudaFuncSetAttribute(attention_decode_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) \
+      if (cudaFuncSetAttribute(attention_decode_kernel<HD_, S_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) \
         return leb_fail("leb_attention_decode: %d bytes of shared memory per block refused", smem); \
       set = true;                                                                                 \
     }                                                                                             \
-  }                                                                                               \
-  leb_launch(attention_decode_kernel<HD_>, grid, dim3(32 * ATD_WARPS), ATD_WARPS * ATD_STAGES(HD_) * 2 * 32 * HD_ * 2, st, \
-      (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,    \
-      bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
-      window, scale, n_splits)
+    leb_launch(attention_decode_kernel<HD_, S_>, grid, dim3(32 * ATD_WARPS), smem, st,             \
+        (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,  \
+        bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
+        window, scale, n_splits);                                                                 \
+  }
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool few = (long)grid.x * grid.y * grid.z <= 2L * n_sm;   // an SM gets two blocks at most: deeper rings
   switch (hd) {
-    case 32: LEB_ATD(32); break;
-    case 64: LEB_ATD(64); break;
-    case 96: LEB_ATD(96); break;
-    default: LEB_ATD(128); break;
+    case 32: LEB_ATD(32, 3); break;
+    case 64: if (few) LEB_ATD(64, 3) else LEB_ATD(64, 2) break;
+    case 96: LEB_ATD(96, 2); break;
+    default: LEB_ATD(128, 2); break;
   }
 #undef LEB_ATD
   LEB_CHECK_LAUNCH("leb_attention_decode");

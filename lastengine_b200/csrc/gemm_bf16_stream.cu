@@ -182,6 +182,20 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
           cv_s[u][k] = (cv_slot[u] >= 0 && k < cv.Lc - 1) ? cv.state[((size_t)cv_slot[u] * D3 + chn) * (cv.Lc - 1) + k] : 0.f;
       }
     }
+    // an adding product: the old values of C (and the next norm's weight) are asked for now and
+    // used after the product, so the tail of the kernel does not wait for them
+    constexpr int EPT = (ROWS * 8 * MT + 32 * ST_WARPS - 1) / (32 * ST_WARPS);   // outputs a thread writes per tile
+    float c_old[EPT], g_next[EPT];
+    if (!CONV && epilogue == 1) {
+#pragma unroll
+      for (int u = 0; u < EPT; u++) {
+        const int idx = threadIdx.x + u * 32 * ST_WARPS;
+        const int col = idx / ROWS, n = tile * ROWS + idx % ROWS;
+        const bool in = idx < ROWS * 8 * MT && col < M && n < N;
+        c_old[u] = in ? to_f32(C[(size_t)col * ldc + n]) : 0.f;
+        g_next[u] = (in && nm.emit_vals) ? nm.emit_g[n] : 0.f;
+      }
+    }
     float acc[NSUB][MT][4];
 #pragma unroll
     for (int s = 0; s < NSUB; s++)
@@ -299,7 +313,10 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
       const int n0 = tile * ROWS;
       // ROWS * 8 * MT is a multiple of the block's threads or smaller than them, and ROWS a multiple
       // of 16: the 16 lanes of a half-warp hold 16 consecutive columns of one row, all or none
-      for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {
+#pragma unroll
+      for (int u = 0; u < EPT; u++) {
+        const int idx = threadIdx.x + u * 32 * ST_WARPS;
+        if (idx >= ROWS * 8 * MT) break;   // whole warps leave together (ROWS * 8 * MT is a multiple of 32)
         const int col = idx / ROWS, rr = idx % ROWS;
         const int n = n0 + rr;
         const bool in = col < M && n < N;
@@ -307,17 +324,16 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
 #pragma unroll
         for (int w = 0; w < ST_WARPS; w++) v += red[w][rr / ST_ROWS][rr % ST_ROWS][col];
         v *= row_scale[col];
-        TC* cp = C + (size_t)col * ldc + n;
         if (in) {
-          if (epilogue == 1) v += to_f32(*cp);
-          *cp = from_f32<TC>(v);
+          if (epilogue == 1) v += c_old[u];
+          C[(size_t)col * ldc + n] = from_f32<TC>(v);
         }
         if (nm.emit_vals) {   // epilogue 1: the new residual, for the norm that follows
           float sq = in ? v * v : 0.f;
 #pragma unroll
           for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-          if (in) nm.emit_vals[(size_t)col * N + n] = __float2bfloat16_rn(v * nm.emit_g[n]);
-          if ((rr & 15) == 0 && col < M && n < N) nm.emit_ssq[(size_t)col * ((N + 15) / 16) + n / 16] = sq;
+          if (in) nm.emit_vals[(size_t)col * N + n] = __float2bfloat16_rn(v * g_next[u]);
+          if ((rr & 15) == 0 && in) nm.emit_ssq[(size_t)col * ((N + 15) / 16) + n / 16] = sq;
         }
       }
     }
@@ -590,8 +606,8 @@ LEB_API int leb_gemm_bf16_stream_conv(void* y, const void* A, const void* W, int
   LEB_REQUIRE(!ssq_in || (parts_in > 0 && d_in > 0), "leb_gemm_bf16_stream_conv: the sums of squares need their count and the row width");
   StreamConv cv{conv_w, bias, state, row_seq, seq_slot, Lc};
   StreamNorm nm{ssq_in, parts_in, d_in, eps, nullptr, nullptr, nullptr};
-  if (M <= 8) return launch_stream<bf16, 1, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
-  return launch_stream<bf16, 2, 3, 3, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
+  if (M <= 8) return launch_stream<bf16, 1, 3, 4, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
+  return launch_stream<bf16, 2, 3, 4, 4>(y, (const bf16*)A, (const bf16*)W, M, 3 * D, K, lda, ldy, 3, st, nm, cv);
 }
 
 template <typename TC>
