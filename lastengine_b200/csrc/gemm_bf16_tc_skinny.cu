@@ -173,14 +173,41 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   }
 }
 
+// The halves of a norm split between two products (see StreamNorm in gemm_bf16_stream.cu), as the
+// second kernel of this product takes them: `ssq_in` scales the rows, `emit_*` leave what the next
+// norm needs (adding epilogue only).
+struct FinishNorm {
+  const float* ssq_in;
+  int parts_in, d_in;
+  float eps;
+  bf16* emit_vals;
+  const float* emit_g;
+  float* emit_ssq;
+};
+
 // Adds the slices in order and applies the epilogue.  part: [slices][M][N] float.
 template <typename TC>
-__global__ void skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, int N, int ldc,
-                                     int epilogue, int n_slices) {
+__global__ void __launch_bounds__(256)
+skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, int N, int ldc, int epilogue,
+                     int n_slices, FinishNorm nm) {
   pdl_wait();
   const int m = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const size_t slab = (size_t)M * N;
+  float r = 1.f;
+  if (nm.ssq_in) {   // the row's factor: every thread of the block takes part
+    __shared__ float warp_part[8];
+    float sum = 0.f;
+    for (int p = threadIdx.x; p < nm.parts_in; p += blockDim.x) sum += nm.ssq_in[(size_t)m * nm.parts_in + p];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) sum += warp_part[w];
+    r = 1.0f / sqrtf(sum / (float)nm.d_in + nm.eps);
+  }
   if (epilogue == 2) {
     // column n = 32*(j/16) + (j%16) is the gate of output j, n + 16 its up value
     if (j >= N / 2) return;
@@ -190,15 +217,29 @@ __global__ void skinny_finish_kernel(TC* __restrict__ C, const float* __restrict
       g += part[s * slab + (size_t)m * N + n];
       u += part[s * slab + (size_t)m * N + n + 16];
     }
+    g *= r;
+    u *= r;
     C[(size_t)m * ldc + j] = from_f32<TC>(g / (1.0f + expf(-g)) * u);
     return;
   }
-  if (j >= N) return;
+  const bool in = j < N;
   float a = 0.f;
-  for (int s = 0; s < n_slices; s++) a += part[s * slab + (size_t)m * N + j];
-  TC* o = C + (size_t)m * ldc + j;
-  if (epilogue == 1) a += to_f32(*o);
-  *o = from_f32<TC>(a);
+  if (in) {
+    for (int s = 0; s < n_slices; s++) a += part[s * slab + (size_t)m * N + j];
+    a *= r;
+    TC* o = C + (size_t)m * ldc + j;
+    if (epilogue == 1) a += to_f32(*o);
+    *o = from_f32<TC>(a);
+  }
+  if (nm.emit_vals) {   // the new residual, for the norm that follows: bf16(x * g) and the sum of x^2 per 16 columns
+    float sq = in ? a * a : 0.f;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (in) {
+      nm.emit_vals[(size_t)m * N + j] = __float2bfloat16_rn(a * nm.emit_g[j]);
+      if ((j & 15) == 0) nm.emit_ssq[(size_t)m * ((N + 15) / 16) + j / 16] = sq;
+    }
+  }
 }
 
 template <int MP>
@@ -238,8 +279,11 @@ LEB_API int leb_gemm_bf16_skinny_supported(const void* A, const void* W, int M, 
 }
 
 // part: float workspace of slices*M*N elements (unused with one slice).
+// The split-norm halves are optional (null): they need at least two slices, since the second kernel applies them.
 LEB_API int leb_gemm_bf16_skinny(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
-                                 int ldc, int epilogue, float* part, int n_slices, int* status, cudaStream_t st) {
+                                 int ldc, int epilogue, float* part, int n_slices, const float* ssq_in, int parts_in,
+                                 int d_in, float eps, void* emit_vals, const float* emit_g, float* emit_ssq, int* status,
+                                 cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_skinny_supported(A, W, M, K, lda), "leb_gemm_bf16_skinny: takes 1..128 rows and TMA-aligned operands (M %d, K %d, lda %d)", M, K, lda);
   LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_skinny: unknown epilogue %d", epilogue);
@@ -247,6 +291,10 @@ LEB_API int leb_gemm_bf16_skinny(void* C, int c_dtype, const void* A, const void
   LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_skinny: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
   LEB_REQUIRE(status != nullptr, "leb_gemm_bf16_skinny: a status word is required");
   if (epilogue == 2 && n_slices < 2) n_slices = 2;   // SwiGLU pairs columns: it is applied by the second kernel
+  LEB_REQUIRE(!(ssq_in || emit_vals) || n_slices >= 2, "leb_gemm_bf16_skinny: a split norm needs at least two slices");
+  LEB_REQUIRE(!emit_vals || (epilogue == 1 && emit_g && emit_ssq), "leb_gemm_bf16_skinny: only an adding product leaves the next norm's input");
+  LEB_REQUIRE(!ssq_in || (parts_in > 0 && d_in > 0), "leb_gemm_bf16_skinny: the sums of squares need their count and the row width");
+  const FinishNorm nm{ssq_in, parts_in, d_in, eps, (bf16*)emit_vals, emit_g, emit_ssq};
   LEB_REQUIRE(n_slices >= 1 && (n_slices == 1 || part), "leb_gemm_bf16_skinny: slices need a workspace");
   const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap mw, mx;
@@ -263,9 +311,9 @@ LEB_API int leb_gemm_bf16_skinny(void* C, int c_dtype, const void* A, const void
   const int cols = epilogue == 2 ? N / 2 : N;
   dim3 grid(ceil_div(cols, 256), M);
   if (c_dtype == LEB_F32)
-    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, (const float*)part, M, N, ldc, epilogue, n_slices);
+    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, (const float*)part, M, N, ldc, epilogue, n_slices, nm);
   else if (c_dtype == LEB_BF16)
-    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, (const float*)part, M, N, ldc, epilogue, n_slices);
+    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, (const float*)part, M, N, ldc, epilogue, n_slices, nm);
   else
     return leb_fail("leb_gemm_bf16_skinny: unknown C dtype %d", c_dtype);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_skinny finish");

@@ -64,7 +64,7 @@ def _declare(L) -> None:
         "leb_attention_prefill": [P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_gemm_bf16_skinny_slices": [I, I],
         "leb_gemm_bf16_skinny_supported": [P, P, I, I, I],
-        "leb_gemm_bf16_skinny": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
+        "leb_gemm_bf16_skinny": [P, I, P, P, I, I, I, I, I, I, P, I, P, I, I, F, P, P, P, P, P],
         "leb_gemm_bf16_tc_supported": [P, P, I, I],
         "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
     }
@@ -372,7 +372,7 @@ class SplitNorm:
 
 
 def split_norm_ok(M: int, dtype: torch.dtype) -> bool:
-    return dtype == torch.bfloat16 and 0 < M <= SMALL_M
+    return dtype == torch.bfloat16 and 0 < M <= SKINNY_M
 
 
 def _scale_args(scale: "SplitNorm | None", M: int, K: int):
@@ -426,25 +426,28 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
         raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
     hint = rows_hint if rows_hint > 0 else M
     tc = _OPTIONAL_TC[0]
+    ssq, parts, d_in, eps = _scale_args(scale, M, K)
+    ev = eg = es = None
+    if emit is not None and group_offsets is None and not streaming and M <= SKINNY_M:
+        assert epilogue == ACCUMULATE and emit.values.shape == (M, N) and emit.ssq.shape == (M, -(-N // 16))
+        assert emit.values.is_contiguous() and emit.ssq.is_contiguous() and emit.weight.numel() == N
+        ev, eg, es = _ptr(emit.values), _ptr(emit.weight), _ptr(emit.ssq)
     if not streaming and group_offsets is None and M <= SMALL_M:
         # the decode step: W streamed through rings of asynchronous copies in shared memory
-        ssq, parts, d_in, eps = _scale_args(scale, M, K)
-        ev = eg = es = None
-        if emit is not None:
-            assert epilogue == ACCUMULATE and emit.values.shape == (M, N) and emit.ssq.shape == (M, -(-N // 16))
-            assert emit.values.is_contiguous() and emit.ssq.is_contiguous() and emit.weight.numel() == N
-            ev, eg, es = _ptr(emit.values), _ptr(emit.weight), _ptr(emit.ssq)
-            emit.filled = True
         _check(L.leb_gemm_bf16_stream(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
                                       epilogue, ssq, parts, d_in, eps, ev, eg, es, _stream()))
+        if ev is not None:
+            emit.filled = True
         return
-    if scale is not None:
-        raise KernelError("linear: a split norm goes with the weight-streaming product of a decode step only")
     # few dozen rows: W as the wide operand with K sliced over blocks, unless N alone already gives
     # every SM several tiles (the output head), where the persistent kernel streams W better
     if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296
-            and linear_skinny(out, x, w, epilogue)):
+            and linear_skinny(out, x, w, epilogue, norm_args=(ssq, parts, d_in, eps, ev, eg, es))):
+        if ev is not None:
+            emit.filled = True
         return
+    if scale is not None:
+        raise KernelError("linear: a split norm goes with the decode products of up to SKINNY_M rows only")
     if (not streaming and group_offsets is None and M >= PAIRS_MIN_ROWS and (N >= 4096 or K >= 4096)
             and linear_tc2(out, x, w, epilogue)):
         return      # many rows and a large weight matrix: 256 x 256 tiles on pairs of SMs
@@ -643,19 +646,23 @@ def _skinny_workspace(device: torch.device, n_floats: int) -> torch.Tensor:
     return bufs[-1]
 
 
-def linear_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE) -> bool:
-    """out (+)= x . w^T for 1..128 rows with W as the wide tcgen05 operand and K sliced over blocks."""
+def linear_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE,
+                  norm_args: tuple | None = None) -> bool:
+    """out (+)= x . w^T for 1..128 rows with W as the wide tcgen05 operand and K sliced over blocks.
+    `norm_args`: the halves of a split norm as `linear` unpacks them (its second kernel applies them)."""
     L = lib()
     M, K = x.shape
     N = w.shape[0]
     if not L.leb_gemm_bf16_skinny_supported(_ptr(x), _ptr(w), M, K, x.stride(0)):
         return False
     slices = L.leb_gemm_bf16_skinny_slices(N, K)
-    if epilogue == SWIGLU:
+    ssq, parts, d_in, eps, ev, eg, es = norm_args or (None, 0, 0, 0.0, None, None, None)
+    if epilogue == SWIGLU or ssq is not None or ev is not None:
         slices = max(slices, 2)
     part = _skinny_workspace(x.device, slices * M * N) if slices > 1 else None
     _check(L.leb_gemm_bf16_skinny(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
-                                  out.stride(0), epilogue, _ptr(part), slices, _ptr(_status_word(x.device)), _stream()))
+                                  out.stride(0), epilogue, _ptr(part), slices, ssq, parts, d_in, eps, ev, eg, es,
+                                  _ptr(_status_word(x.device)), _stream()))
     return True
 
 

@@ -359,11 +359,13 @@ def test_shortconv_decode_fused(B, D, K_, Lc):
             assert float(state[s].min()) == 7.0 and float(state[s].max()) == 7.0
 
 
-@pytest.mark.parametrize("M,D,K_,N2", [(8, 2048, 2048, 6144), (1, 72, 40, 64), (13, 136, 200, 96), (16, 104, 64, 32)])
+@pytest.mark.parametrize("M,D,K_,N2", [(8, 2048, 2048, 6144), (1, 72, 40, 64), (13, 136, 200, 96), (16, 104, 64, 32),
+                                       (64, 2048, 5632, 6144), (17, 72, 40, 64), (100, 136, 200, 96), (128, 104, 64, 32)])
 def test_norm_split_between_two_products(M, D, K_, N2):
     """An RMSNorm split between the product that adds into the residual and the product that reads
     the normed rows (decode steps): the first leaves bfloat16(x * g) and partial sums of x^2, the
-    second scales its sums by rsqrt(mean + eps).  Compared with norm and products in float64."""
+    second scales its sums by rsqrt(mean + eps).  Up to 16 rows through the weight stream, above
+    through the sliced tcgen05 product.  Compared with norm and products in float64."""
     from lastengine_b200.parts.ffn import fuse_gate_up
     eps = 3e-5
     a, w = gen(M, K_, seed=70, dtype=torch.bfloat16), gen(D, K_, seed=71, scale=0.05, dtype=torch.bfloat16)
@@ -386,6 +388,7 @@ def test_norm_split_between_two_products(M, D, K_, N2):
     o2 = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
     K().linear(o2, sp.values, fuse_gate_up(w2[:F], w2[F:], True).to(DEV), K().SWIGLU, scale=sp)
     assert err(o2, P.silu(normed @ w2[:F].double().T) * (normed @ w2[F:].double().T)) < 6e-3
+    K().check_device_status()
 
 
 # ---- rotation and cache write ---------------------------------------------------------------------
