@@ -55,7 +55,7 @@ class PreNormResidualBlock:
     def _normed(self, norm, x, pending, env):
         """norm(x) as the next part's input: the split's values (the part scales its first product),
         or the norm kernel's result."""
-        env.split_out = None             # a producer that did not take its offer leaves none behind
+        env.split_in = env.split_out = None   # nothing is left over from a part that did not take its offer (or raised)
         if pending is not None and pending.filled and pending.weight is norm.weight:
             env.split_in = pending
             return pending.values
