@@ -219,24 +219,66 @@ LEB_API int leb_moe_align(int* offsets, int* sorted_pair, int* pair_row, const i
 }
 
 // x[m, :] (+)= sum_j w[m, j] * ys[pair_row[m*k + j], :]   in the order j = 0..k-1, float.
-__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys,
-                                   const int* __restrict__ pair_row, const float* __restrict__ topk_w,
-                                   int D, int k, int accumulate) {
+// A thread owns VEC consecutive columns of one token; the token's k rows and weights are read
+// first and then all k pieces of ys are asked for before any is used, so the kernel costs two
+// trips to memory whatever k is.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const int* __restrict__ pair_row,
+                   const float* __restrict__ topk_w, int D, int k, int accumulate) {
   pdl_wait();
   const size_t m = blockIdx.x;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    float a = 0.f;
-    for (int j = 0; j < k; j++)
-      a += topk_w[m * k + j] * ys[(size_t)pair_row[m * k + j] * D + i];
-    float* o = x + m * D + i;
-    *o = accumulate ? *o + a : a;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (i >= D) return;
+  int row[MOE_MAX_K];
+  float w[MOE_MAX_K], old[VEC], v[MOE_MAX_K][VEC];
+#pragma unroll
+  for (int j = 0; j < MOE_MAX_K; j++) {
+    row[j] = j < k ? pair_row[m * k + j] : 0;
+    w[j] = j < k ? topk_w[m * k + j] : 0.f;
   }
+  float* o = x + m * D + i;
+  if (VEC == 4) {
+    const float4 t = accumulate ? *reinterpret_cast<const float4*>(o) : make_float4(0.f, 0.f, 0.f, 0.f);
+    old[0] = t.x; old[1 % VEC] = t.y; old[2 % VEC] = t.z; old[3 % VEC] = t.w;
+  } else {
+    old[0] = accumulate ? *o : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < MOE_MAX_K; j++) {
+    if (j < k) {
+      const float* p = ys + (size_t)row[j] * D + i;
+      if (VEC == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[j][0] = t.x; v[j][1 % VEC] = t.y; v[j][2 % VEC] = t.z; v[j][3 % VEC] = t.w;
+      } else {
+        v[j][0] = *p;
+      }
+    }
+  }
+  float a[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; e++) a[e] = 0.f;
+#pragma unroll
+  for (int j = 0; j < MOE_MAX_K; j++)
+    if (j < k)
+#pragma unroll
+      for (int e = 0; e < VEC; e++) a[e] += w[j] * v[j][e];
+  if (VEC == 4)
+    *reinterpret_cast<float4*>(o) = accumulate ? make_float4(old[0] + a[0], old[1 % VEC] + a[1 % VEC], old[2 % VEC] + a[2 % VEC], old[3 % VEC] + a[3 % VEC])
+                                               : make_float4(a[0], a[1 % VEC], a[2 % VEC], a[3 % VEC]);
+  else
+    *o = accumulate ? old[0] + a[0] : a[0];
 }
 
 LEB_API int leb_moe_combine(float* x, const float* ys, const int* pair_row, const float* topk_w,
                             int M, int D, int k, int accumulate, cudaStream_t st) {
   if (M <= 0) return 0;
-  leb_launch(moe_combine_kernel, dim3(M), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+  LEB_REQUIRE(k >= 1 && k <= MOE_MAX_K, "leb_moe_combine: %d rows per token outside 1..%d", k, MOE_MAX_K);
+  if (D % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)ys & 15) == 0)
+    leb_launch(moe_combine_kernel<4>, dim3(M, ceil_div(D, 1024)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+  else
+    leb_launch(moe_combine_kernel<1>, dim3(M, ceil_div(D, 256)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
   LEB_CHECK_LAUNCH("leb_moe_combine");
   return 0;
 }
