@@ -363,8 +363,9 @@ class SplitNorm:
     `values` [M, D] is bfloat16(x * weight) and `ssq` [M, ceil(D/16)] holds partial sums of x^2,
     both left by the product that added into the residual x (`linear(..., emit=...)`); the product
     that takes `values` as its input multiplies its float sums by rsqrt(sum(ssq) / D + eps)
-    (`linear(..., scale=...)`).  Only the weight-streaming product of up to SMALL_M rows does
-    either; `split_norm_ok` says whether a step qualifies."""
+    (`linear(..., scale=...)`).  The products of steps of up to SKINNY_M rows do both (the weight
+    stream up to SMALL_M rows, the sliced tcgen05 product above, in its second kernel);
+    `split_norm_ok` says whether a step qualifies."""
 
     def __init__(self, values: torch.Tensor, ssq: torch.Tensor, weight: torch.Tensor, eps: float):
         self.values, self.ssq, self.weight, self.eps = values, ssq, weight, float(eps)
