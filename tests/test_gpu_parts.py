@@ -221,6 +221,73 @@ def test_toy_parts_register_build_and_step():
         ARCHITECTURES.unregister("ToyForCausalLM")
 
 
+def test_toy_part_takes_part_in_split_norms():
+    """A feed-forward defined here that says `split_norm = True` and passes the two halves on to its
+    products: in decode steps the block then splits the norms around it (no norm kernel between
+    the conv mixer and it, nor between it and the next layer's mixer).  The same model with the
+    part saying False runs the norm kernels; both agree with each other and, token by token, with
+    the whole prompt."""
+    from lastengine_b200 import Engine
+    from lastengine_b200.ops import kernels
+    from lastengine_b200.parts.base import MATRIX, FeedForward, LayerSpec, ModelPlan, PartSpec, ScheduleEntry, TensorSpec
+    from lastengine_b200.registry import ARCHITECTURES, FEED_FORWARDS
+
+    calls = {"scaled": 0, "emitted": 0}
+
+    class TwoMatrices(FeedForward):
+        def __init__(self, hidden_size, inner):
+            self.D, self.F = hidden_size, inner
+
+        def tensors(self):
+            return {"a.weight": TensorSpec((self.F, self.D), MATRIX), "b.weight": TensorSpec((self.D, self.F), MATRIX)}
+
+        def load(self, tensors, env):
+            self.a, self.b = tensors["a.weight"].contiguous(), tensors["b.weight"].contiguous()
+
+        def forward(self, h, out, accumulate, batch, env):
+            scale, emit = env.take_split_in(), env.take_split_out()
+            calls["scaled"] += scale is not None
+            calls["emitted"] += emit is not None
+            t = env.workspace.get("toy.t", (h.shape[0], self.F), env.dtype)
+            kernels.linear(t, h, self.a, scale=scale)
+            kernels.linear(out, t, self.b, kernels.ACCUMULATE if accumulate else kernels.STORE,
+                           emit=emit if accumulate else None)
+
+    def plan_of(kind):
+        def plan(raw):
+            D, V = raw["hidden_size"], raw["vocab_size"]
+            norm = PartSpec("rmsnorm", {"size": D, "eps": 1e-5})
+            layer = lambda i: LayerSpec(f"layers.{i}", PartSpec("shortconv", {"hidden_size": D, "L_cache": 3}),
+                                        PartSpec(kind, {"hidden_size": D, "inner": 80}), norm, norm,
+                                        names={"mixer": "conv", "ffn": "mlp", "mixer_norm": "n1", "ffn_norm": "n2"})
+            return ModelPlan("Toy2ForCausalLM", D, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": D}),
+                             norm, PartSpec("linear_head", {"vocab_size": V, "hidden_size": D, "tied": True}),
+                             layers=[layer(0), layer(1)], schedule=[ScheduleEntry(0), ScheduleEntry(1)],
+                             names={"embedding": "emb", "final_norm": "norm_f", "head": "head"})
+        return plan
+
+    cfg = {"architectures": ["Toy2ForCausalLM"], "hidden_size": 48, "vocab_size": 60}
+    toks = H.requests_for(cfg, [50], 8)[0]
+    got = {}
+    try:
+        for split in (True, False):
+            part = type("TwoMatricesSplit" if split else "TwoMatricesPlain", (TwoMatrices,), {"split_norm": split})
+            FEED_FORWARDS.register("toy_two_matrices", replace=True)(part)
+            ARCHITECTURES.register("Toy2ForCausalLM", replace=True)(plan_of("toy_two_matrices"))
+            eng = Engine.from_config(cfg, seed=4, dtype="bfloat16", max_tokens=512, norm_init="random")
+            calls["scaled"] = calls["emitted"] = 0
+            got[split] = (H.run_whole(eng, toks), H.run_tail(eng, toks, 30))
+            if split:
+                assert calls["scaled"] > 0 and calls["emitted"] > 0      # the block did hand it the halves
+            else:
+                assert calls["scaled"] == 0 and calls["emitted"] == 0
+            assert err(got[split][1], got[split][0]) < 3e-2
+        assert err(got[True][0], got[False][0]) < 3e-2 and err(got[True][1], got[False][1]) < 3e-2
+    finally:
+        FEED_FORWARDS.unregister("toy_two_matrices")
+        ARCHITECTURES.unregister("Toy2ForCausalLM")
+
+
 def test_layer_reads_another_layers_cache(tmp_path):
     """A schedule in which the second attention layer keeps no keys of its own and attends over the
     first one's: it must equal the plain computation with the first layer's keys and values."""
