@@ -251,6 +251,9 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--only-prefill", action="store_true", help="time the prompt step only (for profiling)")
     ap.add_argument("--only-decode", action="store_true", help="skip the prompt timing (for profiling)")
+    ap.add_argument("--unequal", type=int, default=0, metavar="N",
+                    help="instead of the contract's run: N requests with prompts of U[64, 2048] tokens generate "
+                         "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -285,6 +288,23 @@ def main() -> int:
     from lastengine_b200.config import Lfm3Config
     tc = Lfm3Config.from_dict(cfg)
     print(f"[bench] model ready in {time.time() - t0:.1f}s: {nums['weight_bytes'] / 1e9:.3f} GB of weights", file=sys.stderr)
+
+    if args.unequal > 0:
+        # a batch of prompts of unequal lengths through Engine.generate: prompt tokens / time to the first
+        # tokens, decoded tokens / the time after (the reference's definitions, src/server/mod.rs:270-286)
+        from lastengine_b200 import SamplingParams
+        lens = rng.integers(64, 2049, size=args.unequal)
+        prompts = [rng.integers(0, eng.vocab_size, size=int(n)).tolist() for n in lens]
+        greedy = SamplingParams(temperature=0.0)
+        eng.generate([p[:32] for p in prompts], greedy, max_new_tokens=4, stop_token_ids=[], max_batch=args.unequal,
+                     max_seq_len=2048 + args.steps + 1)     # captures the graph of this batch size
+        res = eng.generate(prompts, greedy, max_new_tokens=args.steps, stop_token_ids=[], max_batch=args.unequal,
+                           max_seq_len=2048 + args.steps + 1)
+        st = res.stats
+        print(json.dumps({"scenario": f"{args.unequal} prompts of U[64, 2048] tokens, {args.steps} tokens each, one batch",
+                          "model": model_name, "prompt_tokens": int(lens.sum()), "prefill_tok_s": st.prefill_tok_s,
+                          "decode_tok_s": st.decode_tok_s, "decode_steps": st.decode_steps, "batches": st.batches}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()
