@@ -94,7 +94,14 @@ def _check(rc: int) -> None:
         raise KernelError(lib().leb_last_error().decode())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (torch's raw accessor where it has one: a launch from Python
+    costs some 25 us otherwise, most of it the Stream object)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
