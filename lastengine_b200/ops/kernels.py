@@ -462,7 +462,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
     if tc is not None and not streaming and group_offsets is None and M > SMALL_M and tc(out, x, w, epilogue):
         return
     if (not streaming and group_offsets is not None and E <= 256 and M > 16 * E and w.is_contiguous()
-            and L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, lda)):
+            and _tma_ok(x, w, K)):
         # experts with many rows each (prompts): tcgen05 tiles over the experts' row ranges
         _check(L.leb_gemm_bf16_tc_grouped(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc,
                                           epilogue, _ptr(group_offsets), E, _ptr(_status_word(x.device)), _stream()))
@@ -613,12 +613,17 @@ def check_device_status() -> None:
                               "its result is not valid")
 
 
+def _tma_ok(x: torch.Tensor, w: torch.Tensor, K: int) -> bool:
+    """What leb_gemm_bf16_tc_supported checks (16-byte aligned bases and row strides), without the call."""
+    return K > 0 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
 def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = STORE) -> bool:
     """out (+)= x . w^T on tcgen05 with TMA-fed tiles; False when the operands cannot go through TMA."""
     L = lib()
     M, K = x.shape
     N = w.shape[0]
-    if not L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, x.stride(0)):
+    if not _tma_ok(x, w, K):
         return False
     _check(L.leb_gemm_bf16_tc(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                               out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
@@ -633,7 +638,7 @@ def linear_tc2(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: in
     L = lib()
     M, K = x.shape
     N = w.shape[0]
-    if not L.leb_gemm_bf16_tc_supported(_ptr(x), _ptr(w), K, x.stride(0)):
+    if not _tma_ok(x, w, K):
         return False
     _check(L.leb_gemm_bf16_tc2(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                                out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
@@ -661,7 +666,7 @@ def linear_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue:
     L = lib()
     M, K = x.shape
     N = w.shape[0]
-    if not L.leb_gemm_bf16_skinny_supported(_ptr(x), _ptr(w), M, K, x.stride(0)):
+    if not (1 <= M <= SKINNY_M and _tma_ok(x, w, K)):
         return False
     slices = L.leb_gemm_bf16_skinny_slices(N, K)
     ssq, parts, d_in, eps, ev, eg, es = norm_args or (None, 0, 0, 0.0, None, None, None)
