@@ -160,6 +160,25 @@ def test_a_sequence_goes_out_as_bytes_and_comes_back_in_other_pages():
     c.check()
 
 
+def test_workspace_keeps_addresses_and_hands_out_the_same_views():
+    from lastengine_b200.engine.workspace import Workspace
+    ws = Workspace(torch.device("cpu"))
+    a = ws.get("x", (4, 8), torch.float32)
+    assert ws.get("x", (4, 8), torch.float32) is a                     # the same request: the same tensor
+    b = ws.get("x", (2, 8), torch.bfloat16)                             # another shape and type under the name: same storage
+    assert b.data_ptr() == a.data_ptr() and b.shape == (2, 8) and b.dtype == torch.bfloat16
+    gen = ws.generation
+    a.fill_(3.0)
+    big = ws.get("x", (64, 8), torch.float32)                           # does not fit: new storage, graphs are told
+    assert ws.generation == gen + 1 and big.data_ptr() != a.data_ptr()
+    again = ws.get("x", (4, 8), torch.float32)                          # the old view is not handed out again
+    assert again is not a and again.data_ptr() == big.data_ptr()
+    ws.frozen = True
+    assert ws.get("x", (4, 8), torch.float32) is again
+    with pytest.raises(RuntimeError, match="would grow"):
+        ws.get("x", (1024, 8), torch.float32)
+
+
 def test_xorshift_matches_the_reference_recurrence():
     g = XorShift64(None)
     assert g.state == 0x9E3779B97F4A7C15
