@@ -27,7 +27,7 @@ def lfm3_plan(cfg: Lfm3Config) -> ModelPlan:
     layers: list[LayerSpec] = []
     for l, kind in enumerate(cfg.layer_types):
         if kind == CONV:
-            mixer = PartSpec("shortconv", {"hidden_size": D, "L_cache": cfg.conv_L_cache})
+            mixer = PartSpec("shortconv", {"hidden_size": D, "L_cache": cfg.conv_L_cache, "bias": cfg.conv_bias})
             mixer_name = "conv"
         else:
             sliding = kind == SLIDING
@@ -36,7 +36,9 @@ def lfm3_plan(cfg: Lfm3Config) -> ModelPlan:
                 "hidden_size": D, "num_heads": cfg.num_attention_heads,
                 "num_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                 "norm_eps": cfg.norm_eps, "qk_norm": True,
-                "position": PartSpec("rope", {"rope_dim": cfg.rope_dim, "theta": theta, "style": "neox"}),
+                # the model's frequency factors divide the angles of layers without a window (src/dense.rs:125)
+                "position": PartSpec("rope", {"rope_dim": cfg.rope_dim, "theta": theta, "style": "neox",
+                                              "freq_factors": not sliding}),
                 "window": cfg.sliding_window if sliding else 0,
                 "output_gate": cfg.attn_output_gate})
             mixer_name = "self_attn"
@@ -68,8 +70,4 @@ def lfm3_plan(cfg: Lfm3Config) -> ModelPlan:
 
 @ARCHITECTURES.register(*NAMES)
 def build_lfm3(raw: dict) -> ModelPlan:
-    cfg = Lfm3Config.from_dict(raw)
-    if cfg.conv_bias:
-        from ..config.base import ConfigError
-        raise ConfigError("config.json: 'conv_bias' = true is not supported (the short convolution has no bias terms)")
-    return lfm3_plan(cfg)
+    return lfm3_plan(Lfm3Config.from_dict(raw))

@@ -45,13 +45,20 @@ class Model:
         specs: dict[str, TensorSpec] = {}
         for prefix, part in self.named_parts():
             for rel, spec in part.tensors().items():
-                specs[f"{prefix}.{rel}"] = spec
+                name = spec.shared_name or f"{prefix}.{rel}"
+                if name in specs and specs[name] != spec:
+                    raise ValueError(f"tensor '{name}' is declared twice, as {specs[name]} and as {spec}")
+                specs[name] = spec
         return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         """`tensors`: canonical name -> tensor on the device in the dtype of its role."""
         for prefix, part in self.named_parts():
-            own = {rel: tensors[f"{prefix}.{rel}"] for rel in part.tensors() if f"{prefix}.{rel}" in tensors}
+            own = {}
+            for rel, spec in part.tensors().items():
+                name = spec.shared_name or f"{prefix}.{rel}"
+                if name in tensors:
+                    own[rel] = tensors[name]
             part.load(own, self.env)
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding)

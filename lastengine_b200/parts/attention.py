@@ -54,6 +54,8 @@ class AttentionMixer(Mixer):
                 t["k_layernorm.weight"] = TensorSpec((hd,), NORM)
         if self.output_gate:
             t["gate_proj.weight"] = TensorSpec((nh, D), MATRIX)
+        for name, spec in self.position.tensors().items():
+            t[f"position.{name}"] = spec
         return t
 
     def cache_spec(self):
@@ -70,7 +72,7 @@ class AttentionMixer(Mixer):
         if self.qk_norm:
             self.q_norm_w = tensors["q_layernorm.weight"].contiguous()
             self.k_norm_w = tensors["k_layernorm.weight"].contiguous() if self.own_kv else None
-        self.position.load({}, env)
+        self.position.load({n[len("position."):]: v for n, v in tensors.items() if n.startswith("position.")}, env)
 
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         nh, nkv, hd = self.nh, self.nkv, self.hd
@@ -96,10 +98,25 @@ class AttentionMixer(Mixer):
         if self.output_gate:
             gate = proj[:, col: col + nh]
         q = ws.get("attn.q", (M, nh * hd), env.dtype)
-        pe = self.position
-        kernels.qk_rope_store(q, q_in, k_in, v_in, cache.k if writes else None, cache.v if writes else None,
-                              cache.block_table, batch, self.q_norm_w, self.k_norm_w if writes else None,
-                              self.eps, pe.inv_freq, pe.rope_dim, pe.neox, nh, nkv, hd, cache.page_size)
+        kp, vp = (cache.k, cache.v) if writes else (None, None)
+        rotary = self.position.fused_rotary()
+        if rotary is not None:
+            # per-head norm, rotation and the cache write in one launch
+            kernels.qk_rope_store(q, q_in, k_in, v_in, kp, vp, cache.block_table, batch, self.q_norm_w,
+                                  self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, hd, cache.page_size)
+        else:
+            # an encoding of the part's own: norm, then the part on the normed q and k, then the store
+            qn = ws.get("attn.qn", (M, nh * hd), env.dtype)
+            kernels.qk_rope_store(qn, q_in, None, None, None, None, cache.block_table, batch, self.q_norm_w, None,
+                                  self.eps, None, 0, True, nh, nkv, hd, cache.page_size)
+            kn = None
+            if writes:
+                kn = ws.get("attn.kn", (M, nkv * hd), env.dtype)
+                kernels.qk_rope_store(kn, k_in, None, None, None, None, cache.block_table, batch, self.k_norm_w, None,
+                                      self.eps, None, 0, True, nkv, nkv, hd, cache.page_size)
+            self.position.apply(qn.view(M, nh, hd), kn.view(M, nkv, hd) if writes else None, batch.row_pos)
+            kernels.qk_rope_store(q, qn, kn, v_in, kp, vp, cache.block_table, batch, None, None, self.eps,
+                                  None, 0, True, nh, nkv, hd, cache.page_size)
         o = ws.get("attn.o", (M, nh * hd), env.dtype)
         n_splits = kernels.attention_splits(batch, nkv, nh // nkv)
         scratch = None

@@ -22,7 +22,10 @@ FeedForward:
 Norm:
     forward(out, x, rows=None, add=False)          x float; out in any activation dtype
 PositionEncoding:
-    table() -> float tensor the mixer's kernels use, and its constants as attributes
+    fused_rotary() -> (inv_freq, rope_dim, neox)   a rotation that the mixer's kernel applies itself
+                      | None                       while it norms q and k and stores k and v, or
+    apply(q, k, row_pos)                           any other encoding, in place on the normed
+                                                   q [rows, heads, head_dim] and k [rows, kv heads, head_dim]
 """
 from __future__ import annotations
 
@@ -47,6 +50,8 @@ class TensorSpec:
     role: str
     std: float | None = None      # random init: normal(0, std); None: the model's default
     optional: bool = False        # may be absent from the checkpoint
+    shared_name: str | None = None  # the tensor's full name where it belongs to the model, not to the
+                                    # part's prefix (several parts may then name the same tensor)
 
 
 @dataclass(frozen=True)
@@ -109,6 +114,7 @@ class ModelPlan:
     layers: list[LayerSpec]
     schedule: list[ScheduleEntry]
     init_std: float = 0.02
+    init_stds: dict[str, float] = field(default_factory=dict)   # tensor-name suffix -> std, before init_std
     eos_token_ids: tuple[int, ...] = ()
     names: dict[str, str] = field(default_factory=dict)   # prefixes of embedding / final_norm / head
     tensor_aliases: Any = None     # callable: checkpoint name -> canonical name (or None)
@@ -172,4 +178,20 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, h, out, accumulate, batch, env) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How a mixer's queries and keys learn their positions.  A part either names a rotation the
+    mixer's fused kernel can apply (`fused_rotary`), or encodes q and k itself (`apply`); the
+    mixer asks in this order and knows nothing else about the encoding."""
+
+    def fused_rotary(self):
+        """(inverse frequencies [rope_dim/2] float or None for no rotation, rope_dim, split-half
+        pairing?) when the encoding is a rotation by position * frequency; None otherwise."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor | None, row_pos: torch.Tensor) -> None:
+        """Encodes in place: q [rows, heads, head_dim], k [rows, kv heads, head_dim] (None when the
+        layer stores no keys), row_pos int32 [rows] absolute positions."""
         raise NotImplementedError

@@ -66,12 +66,14 @@ def load_model_dir(model, model_dir: str) -> None:
 def load_random(model, seed: int, norm_init: str = "ones", round_to: torch.dtype | None = torch.bfloat16) -> None:
     """Random weights made on the model's device (no file).  `round_to` rounds the values as a
     folder of that dtype would, so a float32 engine and a bfloat16 engine see the same numbers."""
-    from .random_init import random_tensor, storage_dtype
+    from .random_init import random_tensor, std_for, storage_dtype
 
     plan, env = model.plan, model.env
     tensors = {}
     for name, spec in model.tensor_specs().items():
-        t = random_tensor(name, spec, seed, plan.init_std, norm_init, device=env.device)
+        if spec.optional:
+            continue
+        t = random_tensor(name, spec, seed, std_for(plan, name), norm_init, device=env.device)
         if round_to is not None:
             t = t.to(storage_dtype(spec, round_to))
         tensors[name] = t.to(kept_dtype(spec, t.dtype, env.dtype))

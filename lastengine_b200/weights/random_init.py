@@ -1,7 +1,9 @@
 """Seeded random weights for a model plan, and the writing of a model folder.
 
 Matrices, the embedding and the convolution taps are normal(0, std); norm weights are 1;
-the router's expert bias is normal(0, 0.1).  Each tensor has its own generator seeded from
+the router's expert bias is normal(0, 0.1); other biases are 0.  The std is the tensor's own
+where its part names one, else the plan's entry for the tensor's name (`ModelPlan.init_stds`,
+by suffix), else the plan's default.  Tensors a checkpoint may leave out are left out.  Each tensor has its own generator seeded from
 (seed, tensor name), so the values do not depend on the order of creation.  The reference has
 no such mode (it needs a GGUF file).
 """
@@ -38,6 +40,13 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, std: float, norm_init:
     return s * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=dev)
 
 
+def std_for(plan: ModelPlan, name: str) -> float:
+    for suffix, std in plan.init_stds.items():
+        if name.endswith(suffix):
+            return float(std)
+    return plan.init_std
+
+
 def storage_dtype(spec: TensorSpec, dtype: torch.dtype) -> torch.dtype:
     """Biases are stored in 32-bit; everything else in the folder's dtype."""
     return torch.float32 if spec.role == BIAS else dtype
@@ -61,7 +70,9 @@ def write_model_dir(config: dict, out_dir: str, seed: int, dtype: str = "bfloat1
     model = Model(plan, BuildEnv(device=torch.device("cpu"), dtype=dt))
     tensors = {}
     for name, spec in model.tensor_specs().items():
-        t = random_tensor(name, spec, seed, plan.init_std, norm_init)
+        if spec.optional:
+            continue
+        t = random_tensor(name, spec, seed, std_for(plan, name), norm_init)
         tensors[checkpoint_name(plan, name)] = t.to(storage_dtype(spec, dt))
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "config.json"), "w") as f:

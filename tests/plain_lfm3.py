@@ -76,12 +76,17 @@ def sigmoid(x: torch.Tensor) -> torch.Tensor:
     return 1.0 / (1.0 + torch.exp(-x))
 
 
-def rope(v: torch.Tensor, positions: torch.Tensor, rope_dim: int, theta: float, neox: bool = True) -> torch.Tensor:
+def rope(v: torch.Tensor, positions: torch.Tensor, rope_dim: int, theta: float, neox: bool = True,
+         freq_factors: torch.Tensor | None = None) -> torch.Tensor:
     """src/dense.rs:103-111.  v: [T, heads, head_dim]; pairs (i, i+half) when neox, else (2i, 2i+1);
-    angle = pos * theta^(-2i/rope_dim); a' = a cos - b sin, b' = a sin + b cos."""
+    angle = pos * theta^(-2i/rope_dim) / freq_factors[i] (:106; no factors: 1); a' = a cos - b sin,
+    b' = a sin + b cos."""
     half = rope_dim // 2
-    i = torch.arange(half, dtype=v.dtype)
-    th = positions.to(v.dtype)[:, None] * torch.pow(torch.tensor(theta, dtype=v.dtype), -(2.0 * i) / rope_dim)[None, :]
+    i = torch.arange(half, dtype=v.dtype, device=v.device)
+    th = positions.to(v.dtype)[:, None] * torch.pow(torch.tensor(theta, dtype=v.dtype, device=v.device),
+                                                    -(2.0 * i) / rope_dim)[None, :]
+    if freq_factors is not None:
+        th = th / freq_factors.to(v.dtype)[None, :]
     s, c = torch.sin(th)[:, None, :], torch.cos(th)[:, None, :]
     out = v.clone()
     if neox:
@@ -95,22 +100,24 @@ def rope(v: torch.Tensor, positions: torch.Tensor, rope_dim: int, theta: float, 
     return out
 
 
-def attention(h, p, T, *, nh, nkv, hd, eps, theta, rope_dim, window=0, gate=False, rnd=identity, pos0=0):
-    """src/dense.rs:113-152.  h: [T, D]; p: the layer's tensors by short name."""
+def attention(h, p, T, *, nh, nkv, hd, eps, theta, rope_dim, window=0, gate=False, rnd=identity, pos0=0,
+              freq_factors=None):
+    """src/dense.rs:113-152.  h: [T, D]; p: the layer's tensors by short name.  `freq_factors`: the
+    model's `rope_freqs.weight`, which the caller hands over for layers without a window only (:125)."""
     q = rnd(h @ p["q_proj.weight"].T).view(T, nh, hd)
     k = rnd(h @ p["k_proj.weight"].T).view(T, nkv, hd)
     v = rnd(h @ p["v_proj.weight"].T).view(T, nkv, hd)
     q = rms_norm(q, p["q_layernorm.weight"], eps)          # :119-123, per head over head_dim, before rope
     k = rms_norm(k, p["k_layernorm.weight"], eps)
-    pos = torch.arange(pos0, pos0 + T)
-    q = rnd(rope(q, pos, rope_dim, theta))
-    k = rnd(rope(k, pos, rope_dim, theta))                  # :126-128: the cache holds rotated keys
+    pos = torch.arange(pos0, pos0 + T, device=h.device)
+    q = rnd(rope(q, pos, rope_dim, theta, freq_factors=freq_factors))
+    k = rnd(rope(k, pos, rope_dim, theta, freq_factors=freq_factors))   # :126-128: the cache holds rotated keys
     G = nh // nkv
-    out = torch.zeros(T, nh, hd, dtype=h.dtype)
+    out = torch.zeros(T, nh, hd, dtype=h.dtype, device=h.device)
     for hh in range(nh):
         kvh = hh // G                                       # :133
         sc = (q[:, hh, :] @ k[:, kvh, :].T) / math.sqrt(hd)  # :136
-        t = torch.arange(T)
+        t = torch.arange(T, device=h.device)
         allowed = t[None, :] <= t[:, None]                  # keys up to the query's own position
         if window > 0:                                      # :130: t0 = n - window when n > window, n = pos+1
             allowed &= t[None, :] > t[:, None] - window
@@ -129,14 +136,18 @@ def attention(h, p, T, *, nh, nkv, hd, eps, theta, rope_dim, window=0, gate=Fals
 def short_conv(h, p, T, *, D, Lc, rnd=identity, state=None):
     """src/dense.rs:153-170.  bcx = in_proj h; B = bcx[:D], C = bcx[D:2D], x = bcx[2D:];
     bx = B*x; acc_t = sum_k s[k] w[ch,k] + bx_t w[ch,Lc-1] with s the previous Lc-1 values of bx
-    (zeros at the start); y = C*acc; out = out_proj y."""
+    (zeros at the start); y = C*acc; out = out_proj y.  The reference has no bias; where the
+    checkpoint has `conv.bias` [D] (config key conv_bias) it is the depthwise convolution's own:
+    acc_t = bias[ch] + the taps' sum."""
     bcx = rnd(h @ p["in_proj.weight"].T)
     B, C, xg = bcx[:, :D], bcx[:, D:2 * D], bcx[:, 2 * D:]
     bx = B * xg
     w = p["conv.weight"].reshape(D, Lc)
-    hist = torch.zeros(Lc - 1, D, dtype=h.dtype) if state is None else state
+    hist = torch.zeros(Lc - 1, D, dtype=h.dtype, device=h.device) if state is None else state
     padded = torch.cat([hist, bx], dim=0)                   # row t+Lc-1 is token t
-    acc = torch.zeros(T, D, dtype=h.dtype)
+    acc = torch.zeros(T, D, dtype=h.dtype, device=h.device)
+    if "conv.bias" in p:
+        acc = acc + p["conv.bias"][None, :]
     for j in range(Lc):
         acc = acc + padded[j:j + T, :] * w[:, j][None, :]   # tap Lc-1 meets the current token (:163)
     y = rnd(C * acc)
@@ -199,8 +210,11 @@ def ffn_width(cfg: dict) -> int:
     return f
 
 
-def forward(cfg: dict, tensors: dict[str, torch.Tensor], tokens, rnd=identity, upto_layer=None):
-    """Logits [T, vocab] of one whole sequence (src/dense.rs:171-197, all positions at once)."""
+def forward(cfg: dict, tensors: dict[str, torch.Tensor], tokens, rnd=identity, upto_layer=None,
+            logit_positions=None):
+    """Logits [T, vocab] of one whole sequence (src/dense.rs:171-197, all positions at once), or of
+    `logit_positions` only (the output matrix is applied to those rows alone).  Runs where the
+    tensors live."""
     D = cfg["hidden_size"]
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
@@ -208,7 +222,9 @@ def forward(cfg: dict, tensors: dict[str, torch.Tensor], tokens, rnd=identity, u
     eps = cfg.get("norm_eps", 1e-5)
     theta = cfg.get("rope_theta", 10000.0)
     T = len(tokens)
-    x = tensors["embed_tokens.weight"][torch.as_tensor(tokens, dtype=torch.long)].clone()
+    dev = tensors["embed_tokens.weight"].device
+    x = tensors["embed_tokens.weight"][torch.as_tensor(tokens, dtype=torch.long, device=dev)].clone()
+    ff_global = tensors.get("rope_freqs.weight")
     sandwich = cfg.get("sandwich_norms", False)
     E = cfg.get("num_experts", 0)
     for l, kind in enumerate(layer_kinds(cfg)):
@@ -224,7 +240,8 @@ def forward(cfg: dict, tensors: dict[str, torch.Tensor], tokens, rnd=identity, u
                           theta=cfg.get("rope_theta_swa", 10000.0) if sliding else theta,
                           rope_dim=cfg.get("rope_dim", hd),
                           window=cfg.get("sliding_window", 0) if sliding else 0,
-                          gate=cfg.get("attn_output_gate", False), rnd=rnd)
+                          gate=cfg.get("attn_output_gate", False), rnd=rnd,
+                          freq_factors=None if sliding else ff_global)                # :125
         if sandwich:
             m = rms_norm(m, p["post_mixer_norm.weight"], eps)                     # :185
         x = x + m                                                                 # :186
@@ -241,6 +258,8 @@ def forward(cfg: dict, tensors: dict[str, torch.Tensor], tokens, rnd=identity, u
         x = x + f                                                                 # :193
     if upto_layer is not None:
         return x
+    if logit_positions is not None:
+        x = x[torch.as_tensor(logit_positions, dtype=torch.long, device=dev)]
     xn = rnd(rms_norm(x, tensors["embedding_norm.weight"], eps))                  # :195
     tied = cfg.get("tie_embedding", cfg.get("tie_word_embeddings", True))
     wout = tensors["embed_tokens.weight"] if tied else tensors["lm_head.weight"]  # :196

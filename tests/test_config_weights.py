@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import harness as H  # noqa: F401
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 from lastengine_b200.config import ConfigError, Lfm3Config
 from lastengine_b200.registry import ARCHITECTURES, RegistryError, plan_from_config
@@ -88,7 +88,7 @@ def test_model_folder_roundtrip(tmp_path):
     assert json.load(open(os.path.join(d, "config.json")))["hidden_size"] == 96
     ck = open_checkpoint(d)
     specs = specs_of(TINY_B)
-    assert len(ck) == len(specs) == 172
+    assert len(ck) == len([s for s in specs.values() if not s.optional]) == 172
     f, n = ck["model.layers.1.feed_forward.expert_bias"]
     assert f.dtype(n) == torch.float32                                  # biases are stored in 32-bit
     assert ck["model.embed_tokens.weight"][0].dtype("model.embed_tokens.weight") == torch.bfloat16
@@ -118,6 +118,32 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes():
                    "layers.2.conv.conv.weight: expected [64, 1, 3], found [64, 3]"):
         assert needle in msg, needle
     check_names(specs, {n: s.shape for n, s in specs.items()}, "dir")
+
+
+def test_optional_tensors_frequency_factors_and_conv_bias(tmp_path):
+    """The model's rotary frequency factors are one optional tensor that every attention layer
+    without a window names; a checkpoint fits with it and without it.  `conv_bias` adds a bias
+    tensor per convolution, which a checkpoint must then have."""
+    specs = specs_of(TINY_D)
+    ff = specs["rope_freqs.weight"]
+    assert ff.optional and ff.shape == (8,) and specs["layers.0.conv.conv.bias"].shape == (72,)
+    found = {n: s.shape for n, s in specs.items()}
+    check_names(specs, found, "dir")
+    del found["rope_freqs.weight"]
+    check_names(specs, found, "dir")
+    del found["layers.3.conv.conv.bias"]
+    with pytest.raises(WeightsError, match=r"missing tensors \(1\): layers.3.conv.conv.bias"):
+        check_names(specs, found, "dir")
+    assert "rope_freqs.weight" in specs_of(TINY_A) and "layers.0.conv.conv.bias" not in specs_of(TINY_A)
+    # only layers without a window take the factors (src/dense.rs:125)
+    plan = plan_from_config(TINY_D)
+    assert [l.mixer.params["position"].params["freq_factors"] for l in plan.layers if l.mixer.kind == "attention"] == [True, False]
+    # a written folder leaves the optional tensor out; the test helper adds it
+    d = H.make_model_dir(TINY_D, 3, str(tmp_path / "d"), freq_factors=True)
+    ck = open_checkpoint(d)
+    assert "model.rope_freqs.weight" in ck and len(ck) == len(specs)
+    b = ck["model.layers.0.conv.conv.bias"][0].tensor("model.layers.0.conv.conv.bias")
+    assert b.dtype == torch.float32 and float(b.abs().max()) > 0
 
 
 def test_tied_model_rejects_an_output_matrix():

@@ -6,17 +6,17 @@ import pytest
 import torch
 
 import harness as H
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
-LENGTHS = {"A": [5, 11, 17, 64, 100], "B": [1, 7, 23, 40, 65, 130], "C": [3, 33, 70, 90]}
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+LENGTHS = {"A": [5, 11, 17, 64, 100], "B": [1, 7, 23, 40, 65, 130], "C": [3, 33, 70, 90], "D": [2, 41, 66, 120]}
 
 
 @pytest.fixture(scope="module")
 def model_dirs(tmp_path_factory):
-    return {k: H.make_model_dir(cfg, seed, str(tmp_path_factory.mktemp(f"tiny{k}")))
+    return {k: H.make_model_dir(cfg, seed, str(tmp_path_factory.mktemp(f"tiny{k}")), freq_factors=k == "D")
             for k, (cfg, seed) in CONFIGS.items()}
 
 

@@ -3,6 +3,9 @@ depth, layer pattern, width, head counts and grouping, head size, feed-forward k
 width, vocabulary, rope base, convolution length, eps, tied or own output matrix.
 C is A's shape with the reference's own lfm3 options switched on (norms after mixer and
 feed-forward, per-head output gate, a sliding window with its own rope base).
+D has the two optional tensors: a bias in the short convolution and the model's rotary frequency
+factors (which the layer with a window must not use), three query heads per kv head, a rotation
+over half of the head only, and a convolution of length 5.
 """
 
 TINY_A = {
@@ -38,4 +41,13 @@ TINY_C = {
     "sandwich_norms": True, "attn_output_gate": True,
     "num_experts": 4, "num_experts_per_tok": 1, "moe_intermediate_size": 40, "num_dense_layers": 2,
     "norm_topk_prob": False, "use_expert_bias": False, "routed_scaling_factor": 1.5,
+}
+
+TINY_D = {
+    "architectures": ["Lfm3ForCausalLM"], "model_type": "lfm3",
+    "vocab_size": 300, "hidden_size": 72, "num_hidden_layers": 4,
+    "layer_types": ["conv", "attention", "sliding_attention", "conv"],
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32, "rope_dim": 16,
+    "intermediate_size": 104, "rope_theta": 200000.0, "rope_theta_swa": 30000.0,
+    "sliding_window": 40, "conv_L_cache": 5, "conv_bias": True, "norm_eps": 1e-6, "tie_embedding": False,
 }
