@@ -11,7 +11,7 @@ from __future__ import annotations
 from typing import Sequence
 
 from .config import ConfigError  # noqa: F401
-from .engine.engine import Engine, StepError  # noqa: F401
+from .engine.engine import Engine, EngineOptions, StepError  # noqa: F401
 from .engine.generate import GenerationLoop, GenerationResult, GenerationStats  # noqa: F401
 from .sampling.params import SamplingParams  # noqa: F401
 
@@ -20,14 +20,20 @@ __version__ = "0.1.0"
 
 def generate(engine: Engine, prompts: Sequence[Sequence[int]], sampling: SamplingParams | None = None,
              max_new_tokens: int = 128, stop_token_ids: Sequence[int] | None = None,
-             max_batch: int = 64, max_seq_len: int | None = None, use_graphs: bool = True) -> GenerationResult:
+             max_batch: int = 64, max_seq_len: int | None = None, use_graphs: bool | None = None) -> GenerationResult:
     """Generates for every prompt (lists of token ids), batch after batch.
 
     `stop_token_ids` defaults to the model's `eos_token_id`; a stop token ends its request and
-    is not part of the output.
+    is not part of the output.  `use_graphs` and a sampling seed that the call leaves open come
+    from the engine's options.
     """
+    import dataclasses
     from .engine.generate import EngineBackend
     sampling = sampling or SamplingParams()
+    if sampling.seed is None and engine.options.seed is not None:
+        sampling = dataclasses.replace(sampling, seed=engine.options.seed)
+    if use_graphs is None:
+        use_graphs = engine.options.use_graphs
     stops = tuple(stop_token_ids) if stop_token_ids is not None else tuple(engine.plan.eos_token_ids)
     backend = None
     if use_graphs:

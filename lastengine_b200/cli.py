@@ -53,7 +53,7 @@ def cmd_gpu(a) -> int:
     ids = parse_ids(a.prompt)
     eng = _engine(a.path, a.dtype, a.ctx)
     s = eng.new_sequence()
-    lp = _logprobs(eng.step([s], [ids], "last"))[0]
+    lp = _logprobs(eng.step([s], [ids], "last", check=True))[0]
     eng.release(s)
     top = torch.topk(lp, min(a.top, lp.numel()))
     for i, v in zip(top.indices.tolist(), top.values.tolist()):
@@ -71,7 +71,7 @@ def cmd_tf_dump(a) -> int:
     ids = parse_ids(a.prompt)
     eng = _engine(a.path, a.dtype, a.ctx)
     s = eng.new_sequence()
-    logits = eng.step([s], [ids], "last")
+    logits = eng.step([s], [ids], "last", check=True)
     gen, top = [], []
     for _ in range(a.n):
         lp = _logprobs(logits)[0]
@@ -79,7 +79,7 @@ def cmd_tf_dump(a) -> int:
         top.append([[int(i), float(v)] for i, v in zip(t5.indices.tolist(), t5.values.tolist())])
         nxt = int(t5.indices[0])
         gen.append(nxt)
-        logits = eng.step([s], [[nxt]], "last")
+        logits = eng.step([s], [[nxt]], "last", check=True)
     eng.release(s)
     print(json.dumps({"prompt_ids": ids, "gen_ids": gen, "top": top}))
     return 0
@@ -95,9 +95,9 @@ def cmd_dense_cmp(a) -> int:
     exact = _engine(a.path, "float32", a.ctx)
     fast = _engine(a.path, "bfloat16", a.ctx)
     se, sf = exact.new_sequence(), fast.new_sequence()
-    le = _logprobs(exact.step([se], [ids], "last"))[0].clone()
+    le = _logprobs(exact.step([se], [ids], "last", check=True))[0].clone()
     t0 = time.perf_counter()
-    lf = _logprobs(fast.step([sf], [ids], "last"))[0].clone()
+    lf = _logprobs(fast.step([sf], [ids], "last", check=True))[0].clone()
     torch.cuda.synchronize()
     print(f"bfloat16 prefill {len(ids)} tok in {time.perf_counter() - t0:.3f}s")
     agree, shown, maxd, sumd = 0, 0, 0.0, 0.0
@@ -111,8 +111,8 @@ def cmd_dense_cmp(a) -> int:
             shown += 1
             print(f"step {k}: float32 {ta} lp {float(le[ta]):.3f} (bfloat16 lp {float(lf[ta]):.3f}) vs bfloat16 {tb} "
                   f"lp {float(lf[tb]):.3f} (float32 lp {float(le[tb]):.3f})")
-        le = _logprobs(exact.step([se], [[ta]], "last"))[0].clone()
-        lf = _logprobs(fast.step([sf], [[ta]], "last"))[0].clone()
+        le = _logprobs(exact.step([se], [[ta]], "last", check=True))[0].clone()
+        lf = _logprobs(fast.step([sf], [[ta]], "last", check=True))[0].clone()
     print(f"{agree}/{a.n} argmax agree, mean |dlogprob| {sumd / max(a.n, 1):.4f}, max {maxd:.4f}")
     return 0
 

@@ -98,6 +98,10 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
   const int slot = seq_slot[b];
   const size_t m_row = seq_qstart[b];
   const int h0 = kvh * G;
+  // q, out and the partial results have one row per sequence of the launch (gridDim.y): a row
+  // index beyond that (a seq_qstart taken from a step with several rows per sequence) is skipped
+  // instead of being written past the end of those buffers
+  if (m_row >= gridDim.y) return;
 
   if (slot < 0) {  // padding sequence
     for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {

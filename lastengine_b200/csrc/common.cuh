@@ -101,3 +101,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// SMs of the current device, asked once per device (device_info.cu); launch shapes that are
+// chosen for "a wave of blocks" use it.
+extern "C" int leb_sm_count();
+static inline int sm_count() {
+  int n = leb_sm_count();
+  return n > 0 ? n : 1;
+}

@@ -563,7 +563,7 @@ static int stream_dispatch(void* C, const bf16* a, const bf16* w, int M, int N, 
     return launch_stream<TC, 2, 2, 4, 4>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
   }
   // few tiles (at most one per SM) and a long K: deeper rings instead of a second block per SM
-  if (M <= 8 && ceil_div(N, ST_ROWS) <= 148 && K >= 4096) return launch_stream<TC, 1, 1, 8, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
+  if (M <= 8 && ceil_div(N, ST_ROWS) <= sm_count() && K >= 4096) return launch_stream<TC, 1, 1, 8, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
   if (M <= 8) return launch_stream<TC, 1, 1, 4, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
   return launch_stream<TC, 2, 1, 3, 8>(C, a, w, M, N, K, lda, ldc, epilogue, st, nm);
 }

@@ -16,6 +16,10 @@
 // (one new row per sequence against the paged cache, bfloat16), with the same arguments except
 // that it takes no scratch pointer.  It calls no cudaMalloc, cudaFree or any allocating routine.
 //
+//  * Every sequence brings one row: seq_qstart must be a permutation of 0..B-1 (the row of q and
+//    out that sequence b uses).  A sequence whose seq_qstart is B or more is skipped, so the array
+//    is never written past its end; a row that no sequence names keeps whatever the merge finds
+//    in the array.
 //  * Limit: rows * heads * n_splits * (head_dim + 2) must not exceed
 //    LEB_NO_ALLOC_SCRATCH_FLOATS; beyond that the call fails with a message (leb_last_error)
 //    and launches nothing.  With n_splits == 1 no scratch is used and there is no limit.

@@ -115,7 +115,7 @@ LEB_API int leb_moe_router(int* topk_ids, float* topk_w, const void* h, int dtyp
   LEB_REQUIRE(k >= 1 && k <= MOE_MAX_K && k <= E, "leb_moe_router: top-%d outside 1..min(%d, experts)", k, MOE_MAX_K);
   // rows per block: 1 while every row can have an SM of its own (a block's pace is set by one SM
   // reading the router's weights), 4 for many rows when they fit shared memory
-  const bool four = M > 148 && ((size_t)4 * D + 8 * E) * sizeof(float) <= 48 * 1024;
+  const bool four = M > sm_count() && ((size_t)4 * D + 8 * E) * sizeof(float) <= 48 * 1024;
   const int R = four ? 4 : 1;
   const size_t smem = ((size_t)R * D + 2 * R * E) * sizeof(float);
   LEB_REQUIRE(smem <= 48 * 1024, "leb_moe_router: hidden size %d too large for the router kernel", D);

@@ -255,7 +255,8 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
   if (dtype == LEB_BF16 && inv_freq && neox && rope_dim == hd && (hd == 64 || hd == 128)) {
     // heads per warp: one while the launch is small, up to all of a row's over 8 warps
     int per_warp = 1;
-    while (per_warp * ROPE_WARPS < total && (long long)M * ceil_div(total, per_warp * ROPE_WARPS) > 4 * 148) per_warp++;
+    const long long n_sm = sm_count();
+    while (per_warp * ROPE_WARPS < total && (long long)M * ceil_div(total, per_warp * ROPE_WARPS) > 4 * n_sm) per_warp++;
     dim3 grid(M + tiles, ceil_div(total, per_warp * ROPE_WARPS));
     if (hd == 64)
       leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 2>, grid, block, 0, st,

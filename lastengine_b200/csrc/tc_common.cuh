@@ -33,15 +33,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when it gave up (and *abort is set so that the other roles leave too).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+// Bounded wait: false when it gave up after `limit` polls (and *abort is set so that the other
+// roles leave too).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                uint32_t limit) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (i > 4096) __nanosleep(64);
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, TC_SPIN_LIMIT);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(

@@ -9,6 +9,7 @@ gives the last position's logits and `forward(token)` the next (src/gpu/dense.rs
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass, fields, replace
 from typing import Sequence
 
 import numpy as np
@@ -41,9 +42,42 @@ def resolve_dtype(dtype) -> torch.dtype:
         raise ValueError(f"unknown dtype '{dtype}' (bfloat16, float32)") from None
 
 
+@dataclass(frozen=True)
+class EngineOptions:
+    """What an engine is built with, beside the model.  The reference sets the like through `--ctx`
+    and `LE_*` variables (src/cli.rs:47); its prompt pieces are 512 rows (src/gpu/dense.rs:28,376)."""
+    dtype: str = "bfloat16"            # "bfloat16" or "float32" (true 32-bit arithmetic throughout)
+    max_seqs: int | None = None        # sequences alive at once (default: as many as there are cache pages)
+    max_tokens: int = 8192             # positions all live sequences may hold together, each rounded up to whole pages
+    max_batch_tokens: int = 16384      # rows one pass over the layers takes; a longer step runs in pieces (0: no limit)
+    use_graphs: bool = True            # decode steps of `generate` as captured CUDA graphs
+    seed: int | None = None            # sampling seed for calls whose SamplingParams name none
+    device: str = "cuda:0"
+
+    def __post_init__(self):
+        resolve_dtype(self.dtype)
+        if self.max_tokens < 1 or (self.max_seqs is not None and self.max_seqs < 1) or self.max_batch_tokens < 0:
+            raise ValueError(f"engine options out of range: {self}")
+
+    @staticmethod
+    def of(options: "EngineOptions | None", **overrides) -> "EngineOptions":
+        """`options` (or the defaults) with the given fields replaced; unknown names are an error."""
+        known = {f.name for f in fields(EngineOptions)}
+        bad = sorted(set(overrides) - known)
+        if bad:
+            raise TypeError(f"unknown engine option(s) {bad}; known: {sorted(known)}")
+        if "dtype" in overrides and isinstance(overrides["dtype"], torch.dtype):
+            overrides["dtype"] = {torch.float32: "float32", torch.bfloat16: "bfloat16"}.get(overrides["dtype"], str(overrides["dtype"]))
+        if "device" in overrides:
+            overrides["device"] = str(overrides["device"])
+        return replace(options or EngineOptions(), **overrides)
+
+
 class Engine:
-    def __init__(self, plan: ModelPlan, dtype="bfloat16", max_tokens: int = 8192,
-                 max_seqs: int | None = None, device: str | torch.device = "cuda:0"):
+    def __init__(self, plan: ModelPlan, options: EngineOptions | None = None, **overrides):
+        """`options`, or single fields of it by name (`dtype=`, `max_tokens=`, ...)."""
+        self.options = opt = EngineOptions.of(options, **overrides)
+        dtype, max_tokens, max_seqs, device = opt.dtype, opt.max_tokens, opt.max_seqs, opt.device
         dev = torch.device(device)
         if dev.type != "cuda" or not torch.cuda.is_available():
             raise RuntimeError("lastengine_b200 runs on a CUDA device only (no CPU path); "
@@ -66,23 +100,24 @@ class Engine:
 
     # ---- construction --------------------------------------------------------------------
     @classmethod
-    def from_pretrained(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
+    def from_pretrained(cls, model_dir: str, options: EngineOptions | None = None, **kw) -> "Engine":
         """A folder with config.json and model.safetensors; the model class is chosen by config.json."""
         from ..weights import load_model_dir
         raw = read_config_json(model_dir)
-        eng = cls(plan_from_config(raw), dtype=dtype, **kw)
+        eng = cls(plan_from_config(raw), options, **kw)
         load_model_dir(eng.model, model_dir)
         eng.loaded = True
         eng.config = raw
         return eng
 
     @classmethod
-    def from_config(cls, config: dict | str, seed: int = 0, dtype="bfloat16", norm_init: str = "ones",
-                    **kw) -> "Engine":
-        """Random weights made on the device from a configuration and a seed."""
+    def from_config(cls, config: dict | str, seed: int = 0, options: EngineOptions | None = None,
+                    norm_init: str = "ones", **kw) -> "Engine":
+        """Random weights made on the device from a configuration and a seed (the weights' seed;
+        `EngineOptions.seed` is the sampling seed)."""
         from ..weights import load_random
         raw = read_config_json(config) if isinstance(config, (str, os.PathLike)) else config
-        eng = cls(plan_from_config(raw), dtype=dtype, **kw)
+        eng = cls(plan_from_config(raw), options, **kw)
         load_random(eng.model, seed, norm_init=norm_init)
         eng.loaded = True
         eng.config = raw
@@ -109,11 +144,9 @@ class Engine:
         return self.cache.import_seq(data)
 
     # ---- the step -------------------------------------------------------------------------
-    def prepare(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
-                want: str | Sequence[Sequence[int]] | None = "last",
-                u01: np.ndarray | None = None, builder: BatchBuilder | None = None,
-                table_width: int | None = None, feed: np.ndarray | None = None) -> tuple[StepBatch, dict[int, int]]:
-        """Checks a step, reserves its cache room and lays it out on the device."""
+    def check_step(self, seqs, tokens, want) -> tuple[list[int], list[int]]:
+        """Raises StepError for a step that cannot run; returns (each sequence's length before the
+        step, the step's rows whose logits are wanted)."""
         if not self.loaded:
             raise RuntimeError("the engine has no weights yet")
         if len(seqs) != len(tokens) or len(seqs) == 0:
@@ -146,8 +179,8 @@ class Engine:
         elif want is None:
             rows = []
         else:
-            if len(want) != len(seqs):
-                raise StepError("`want` needs one list of places per sequence")
+            if isinstance(want, str) or len(want) != len(seqs):
+                raise StepError("`want` is \"last\", None, or one list of places per sequence")
             rows, r0 = [], 0
             for t, w in zip(tokens, want):
                 for i in w:
@@ -155,6 +188,15 @@ class Engine:
                         raise StepError(f"wanted place {i} is outside the {len(t)} tokens the sequence brings")
                     rows.append(r0 + i)
                 r0 += len(t)
+        return pos0, rows
+
+    def prepare(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
+                want: str | Sequence[Sequence[int]] | None = "last",
+                u01: np.ndarray | None = None, builder: BatchBuilder | None = None,
+                table_width: int | None = None, feed: np.ndarray | None = None) -> tuple[StepBatch, dict[int, int]]:
+        """Checks a step, reserves its cache room and lays it out on the device."""
+        pos0, rows = self.check_step(seqs, tokens, want)
+        live = [s for s in seqs if s >= 0]
         grow = {s: len(t) for s, t in zip(seqs, tokens) if s >= 0}
         self.cache.reserve(grow)
         tables = {}
@@ -165,17 +207,81 @@ class Engine:
         return b, grow
 
     def step(self, seqs: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: str | Sequence[Sequence[int]] | None = "last") -> torch.Tensor:
+             want: str | Sequence[Sequence[int]] | None = "last", check: bool = False) -> torch.Tensor:
         """Feeds `tokens[i]` to sequence `seqs[i]` and returns float logits [wanted rows, vocab].
 
         `want`: "last" (the last token of each sequence), None (nothing), or per sequence the
         places among its tokens of this step.  The result lives in workspace memory that the
-        next step overwrites: copy it if it must outlive the step.
+        next step overwrites: copy it if it must outlive the step.  A step of more rows than
+        `options.max_batch_tokens` runs in pieces of at most that many rows, one after the other
+        against the cache, with the same result.  `check`: wait for the device and raise
+        KernelError if a kernel of the step gave up on a bounded wait (`check_status`).
         """
-        batch, grow = self.prepare(seqs, tokens, want)
-        logits = self.model.forward(batch, self.cache)
-        self.cache.commit(grow)
+        limit = self.options.max_batch_tokens
+        if limit and sum(len(t) for t in tokens) > limit:
+            logits = self._step_in_pieces(seqs, tokens, want, limit)
+        else:
+            batch, grow = self.prepare(seqs, tokens, want)
+            logits = self.model.forward(batch, self.cache)
+            self.cache.commit(grow)
+        if check:
+            self.check_status()
         return logits
+
+    def check_status(self) -> None:
+        """Waits for the device and raises KernelError if a tensor-core kernel gave up on one of its
+        bounded waits since the last check: what such a step computed is not valid.  The
+        generation loop reads the same word with every step's tokens."""
+        from ..ops import kernels
+        kernels.check_device_status()
+
+    def _step_in_pieces(self, seqs, tokens, want, limit: int) -> torch.Tensor:
+        """The step cut into pieces of at most `limit` rows (a sequence's tokens may be cut too:
+        its later part finds the earlier one in the cache).  Checked and given cache room as a
+        whole first, so that it runs entirely or not at all."""
+        if isinstance(want, str) and want == "last":
+            places = [[len(t) - 1] if len(t) else [] for t in tokens]
+        elif want is None:
+            places = [[] for _ in tokens]
+        else:
+            places = [list(w) for w in want]
+        self.check_step(seqs, tokens, places)
+        self.cache.reserve({s: len(t) for s, t in zip(seqs, tokens) if s >= 0})
+        R = sum(len(w) for w in places)
+        out = self.workspace.get("engine.logits_of_pieces", (R, self.vocab_size), torch.float32)
+        pieces, cur, room = [], [], limit
+        for i, t in enumerate(tokens):
+            lo = 0
+            while lo < len(t):
+                n = min(room, len(t) - lo)
+                cur.append((i, lo, lo + n))
+                lo, room = lo + n, room - n
+                if room == 0:
+                    pieces.append(cur)
+                    cur, room = [], limit
+        if cur:
+            pieces.append(cur)
+        # rows of `out`: in the order of the sequences and of their places, as one step would give them
+        first_row, r = [], 0
+        for w in places:
+            first_row.append(r)
+            r += len(w)
+        for piece in pieces:
+            p_want, dst = [], []
+            for i, lo, hi in piece:
+                p_want.append([k - lo for k in places[i] if lo <= k < hi])
+                dst += [first_row[i] + j for j, k in enumerate(places[i]) if lo <= k < hi]
+            batch, grow = self.prepare([seqs[i] for i, _, _ in piece], [tokens[i][lo:hi] for i, lo, hi in piece], p_want)
+            lg = self.model.forward(batch, self.cache)
+            self.cache.commit(grow)
+            r = 0
+            while r < len(dst):          # runs of consecutive rows go over in one copy
+                e = r + 1
+                while e < len(dst) and dst[e] == dst[e - 1] + 1:
+                    e += 1
+                out[dst[r]:dst[r] + e - r].copy_(lg[r:e])
+                r = e
+        return out
 
     # ---- numbers for reports --------------------------------------------------------------
     def weight_bytes(self) -> int:

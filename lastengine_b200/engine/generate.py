@@ -142,34 +142,46 @@ class GenerationLoop:
                 r.slot = s
             active = batch
             t1 = self.clock()
-            while True:
-                done = []
-                for r, t in zip(active, toks):
-                    t = int(t)
-                    if t in self.stop:                    # not emitted and not fed (src/local.rs:252)
-                        r.reason = "stop"
-                    else:
-                        r.out.append(t)
-                        if len(r.out) >= r.budget:        # emitted, not fed (src/local.rs:262)
-                            r.reason = "length"
-                    if r.reason is not None:
-                        done.append(r)
-                if done:
-                    self.backend.finish([r.slot for r in done])
-                    active = [r for r in active if r.reason is None]
-                if not active:
-                    break
-                u = [r.rng.next() for r in active] if draw else None
-                kw = {}
-                if getattr(self.backend, "lookahead", False):
-                    kw["lookahead"] = ([r.rng.peek() for r in active] if draw else None,
-                                       [len(r.out) + 1 < r.budget for r in active])
-                toks = self.backend.decode([r.slot for r in active], [r.out[-1] for r in active], u,
-                                           [r.history for r in active] if want_hist else None, **kw)
-                stats.decode_steps += 1
-                stats.decode_tokens += len(active)
+            try:
+                active = self._decode_batch(active, toks, stats, draw, want_hist)
+            except BaseException:
+                # a step failed (no cache room, a kernel that gave up): nothing of the batch stays behind
+                held = [r.slot for r in batch if r.reason is None]
+                if held:
+                    getattr(self.backend, "abort", self.backend.finish)(held)
+                raise
             stats.decode_ms += (self.clock() - t1) * 1e3
         return GenerationResult([r.out for r in reqs], [r.reason or "length" for r in reqs], stats)
+
+    def _decode_batch(self, active, toks, stats, draw, want_hist):
+        """One batch from its first tokens until its last request has ended."""
+        while True:
+            done = []
+            for r, t in zip(active, toks):
+                t = int(t)
+                if t in self.stop:                    # not emitted and not fed (src/local.rs:252)
+                    r.reason = "stop"
+                else:
+                    r.out.append(t)
+                    if len(r.out) >= r.budget:        # emitted, not fed (src/local.rs:262)
+                        r.reason = "length"
+                if r.reason is not None:
+                    done.append(r)
+            if done:
+                self.backend.finish([r.slot for r in done])
+                active = [r for r in active if r.reason is None]
+            if not active:
+                break
+            u = [r.rng.next() for r in active] if draw else None
+            kw = {}
+            if getattr(self.backend, "lookahead", False):
+                kw["lookahead"] = ([r.rng.peek() for r in active] if draw else None,
+                                   [len(r.out) + 1 < r.budget for r in active])
+            toks = self.backend.decode([r.slot for r in active], [r.out[-1] for r in active], u,
+                                       [r.history for r in active] if want_hist else None, **kw)
+            stats.decode_steps += 1
+            stats.decode_tokens += len(active)
+        return active
 
 
 class EngineBackend:
@@ -181,31 +193,48 @@ class EngineBackend:
         self.engine = engine
         self.sampler = Sampler(sampling, engine.device)
         self._torch = torch
-        self._out = torch.empty(1024, dtype=torch.int32, device=engine.device)
-        self._host = torch.empty(1024, dtype=torch.int32, pin_memory=True)
+        self._host = torch.empty(1025, dtype=torch.int32, pin_memory=True)
         self.d2h_bytes = 0
 
-    def _choose(self, logits, u01, histories, batch) -> list[int]:
+    def _choose(self, logits, u01_dev, histories) -> list[int]:
+        """Chooses a token per row of `logits` and brings the tokens to the host, the device's
+        status word with them: a step in which a kernel gave up on a bounded wait raises KernelError
+        instead of handing out what it left."""
+        from ..ops import kernels
+        torch, dev = self._torch, self.engine.device
         n = logits.shape[0]
-        if n > self._out.numel():
-            self._out = self._torch.empty(2 * n, dtype=self._torch.int32, device=self.engine.device)
-            self._host = self._torch.empty(2 * n, dtype=self._torch.int32, pin_memory=True)
+        if n + 1 > self._host.numel():
+            self._host = torch.empty(2 * n + 1, dtype=torch.int32, pin_memory=True)
         if histories is not None:
             self.sampler.apply_penalties(logits, histories)
-        self.sampler.sample(self._out, logits, batch.u01)
-        self._host[:n].copy_(self._out[:n], non_blocking=True)
-        self._torch.cuda.current_stream().synchronize()
-        self.d2h_bytes = n * 4
-        return self._host[:n].tolist()
+        if n <= kernels.RESULT_TOKENS:
+            self.sampler.sample(kernels.result_tokens(dev), logits, u01_dev)
+            self._host[:n + 1].copy_(kernels.status_and_tokens(dev, n), non_blocking=True)
+        else:                                      # more rows than the shared buffer holds: two copies
+            out = torch.empty(n, dtype=torch.int32, device=dev)
+            self.sampler.sample(out, logits, u01_dev)
+            self._host[:1].copy_(kernels.status_and_tokens(dev, 0), non_blocking=True)
+            self._host[1:n + 1].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes = (n + 1) * 4
+        vals = self._host[:n + 1].tolist()
+        kernels.raise_on_status(vals[0], dev)
+        return vals[1:]
 
     def _step(self, slots, tokens, u01, histories) -> list[int]:
         import numpy as np
         eng = self.engine
         u = np.asarray(u01, dtype=np.float32) if u01 is not None else None
+        limit = eng.options.max_batch_tokens
+        if limit and sum(len(t) for t in tokens) > limit:
+            # prompts of more rows than one pass takes: the step function cuts them
+            logits = eng.step(slots, tokens, "last")
+            u_dev = self._torch.from_numpy(u).to(eng.device) if u is not None else None
+            return self._choose(logits, u_dev, histories)
         batch, grow = eng.prepare(slots, tokens, "last", u01=u)
         logits = eng.model.forward(batch, eng.cache)
         eng.cache.commit(grow)
-        return self._choose(logits, u01, histories, batch)
+        return self._choose(logits, batch.u01, histories)
 
     def start(self, prompts, u01, histories):
         slots = [self.engine.new_sequence() for _ in prompts]
@@ -220,3 +249,5 @@ class EngineBackend:
 
     def finish(self, slots):
         self.engine.release(slots)
+
+    abort = finish

@@ -36,15 +36,18 @@ class DecodeGraph:
     that feed themselves) the move to the next position."""
 
     def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False,
-                 out: torch.Tensor | None = None, fed: bool = False, history=None):
-        """`out`: where the chosen tokens go (shared between the buckets of one backend, so that a
-        step of one bucket can take its tokens from the step of another).  `fed`: the step begins
-        by taking tokens from `out` where the staged step says so.  `history`: (ring of recent
-        tokens per cache slot [slots, 256], tokens seen per slot) on the device, for the penalties."""
+                 out: torch.Tensor | None = None, fed: bool = False, history=None, workspace: Workspace | None = None):
+        """`table_width`: pages per sequence the step's page tables have; the longest sequence a
+        replay can serve, and the length the split of the decode attention is chosen for.  `out`:
+        where the chosen tokens go (shared between the graphs of one backend, so that a step of
+        one bucket can take its tokens from the step of another).  `fed`: the step begins by
+        taking tokens from `out` where the staged step says so.  `history`: (ring of recent
+        tokens per cache slot [slots, 256], tokens seen per slot) on the device, for the penalties.
+        `workspace`: scratch shared with the other widths of the same bucket."""
         self.history = history
         self.engine, self.sampler, self.bucket, self.width = engine, sampler, bucket, table_width
         self.self_feeding, self.fed = self_feeding, fed
-        self.ws = Workspace(engine.device)
+        self.ws = workspace if workspace is not None else Workspace(engine.device)
         self.builder = BatchBuilder(engine.device)
         self.out = out if out is not None else torch.zeros(bucket, dtype=torch.int32, device=engine.device)
         self.graph: torch.cuda.CUDAGraph | None = None
@@ -52,6 +55,7 @@ class DecodeGraph:
         self.staged_slots: list[int] = []
         self.cache_version = -1
         self.launches = 0
+        self.ws_generation = -1
 
     def _run(self, batch) -> None:
         eng = self.engine
@@ -186,11 +190,14 @@ class GraphBackend(EngineBackend):
     def __init__(self, engine, sampling: SamplingParams, max_batch: int = 64, max_seq_len: int | None = None):
         super().__init__(engine, sampling)
         page = engine.cache.page_size
-        self.width = -(-(max_seq_len or engine.max_tokens) // page)
+        self.max_width = -(-(max_seq_len or engine.max_tokens) // page)
         # Captured graphs outlive one call: they belong to the engine, keyed by what is baked into
-        # them (the sampling constants and the width of the page tables).
+        # them: the sampling constants here, and per graph the bucket and the width of its page
+        # tables.  The width follows the sequences that are live (the next power of two of their
+        # pages), not the cache's capacity: the decode attention chooses its split for the width,
+        # and a short sequence in a large cache must not be split and merged for lengths it has not.
         store = engine.__dict__.setdefault("_decode_graphs", {})
-        self.graphs: dict = store.setdefault((sampling, self.width), {})
+        self.graphs: dict = store.setdefault(sampling, {})
         self.h2d_bytes = 0
         self._ahead: _StepInFlight | None = None
         self._launched = 0
@@ -198,13 +205,27 @@ class GraphBackend(EngineBackend):
         self._fed: dict[int, int] = {}                    # slot -> the token the next step was given on the device
 
     def _chosen(self, n: int) -> torch.Tensor:
+        """Where the steps put their chosen tokens: the buffer behind the device's status word (one
+        copy then brings both to the host), or for very large batches a buffer of the backend's own."""
+        if n <= kernels.RESULT_TOKENS:
+            return kernels.result_tokens(self.engine.device)
         out = self.graphs.get("out")
         if out is None or out.numel() < n:
             # graphs point at the old buffer: they are captured again with the new one
-            for k in [k for k in self.graphs if isinstance(k, int)]:
+            for k in [k for k in self.graphs if isinstance(k, tuple)]:
                 del self.graphs[k]
-            out = self.graphs["out"] = torch.zeros(max(256, n), dtype=torch.int32, device=self.engine.device)
+            out = self.graphs["out"] = torch.zeros(n, dtype=torch.int32, device=self.engine.device)
         return out
+
+    def _width_for(self, slots) -> int:
+        """Pages the step's tables need: the next power of two of what the longest sequence holds
+        after this step, at most the width of the longest sequence allowed."""
+        cache = self.engine.cache
+        need = max(-(-(cache.length(s) + 1) // cache.page_size) for s in slots)
+        w = 1
+        while w < need:
+            w *= 2
+        return max(need, min(w, self.max_width))
 
     def _history(self):
         """The rings of recent tokens per cache slot (made when the sampling has penalties)."""
@@ -221,9 +242,12 @@ class GraphBackend(EngineBackend):
         eng = self.engine
         b = bucket_for(len(slots))
         out = self._chosen(b)
-        g = self.graphs.get(b)
+        width = self._width_for(slots)
+        g = self.graphs.get((b, width))
         if g is None:
-            g = self.graphs[b] = DecodeGraph(eng, self.sampler, b, self.width, out=out, fed=True, history=self._history())
+            ws = self.graphs.setdefault(("scratch", b), Workspace(eng.device))
+            g = self.graphs[(b, width)] = DecodeGraph(eng, self.sampler, b, width, out=out, fed=True,
+                                                      history=self._history(), workspace=ws)
         grow = g.restage(slots, tokens, u01, feed)
         if grow is None:
             grow = g.stage(slots, tokens, u01, feed)
@@ -232,25 +256,33 @@ class GraphBackend(EngineBackend):
         g.cache_version = eng.cache.state_version
         n = len(slots)
         self._launched += 1
-        host = torch.empty(n, dtype=torch.int32, pin_memory=True) if n > 1024 else \
+        host = torch.empty(n + 1, dtype=torch.int32, pin_memory=True) if n > 1024 else \
             self._hosts[self._launched % 2]
-        host[:n].copy_(out[:n], non_blocking=True)
+        # the status word and the tokens: one copy where they lie together
+        if n <= kernels.RESULT_TOKENS:
+            host[:n + 1].copy_(kernels.status_and_tokens(eng.device, n), non_blocking=True)
+        else:
+            host[:1].copy_(kernels.status_and_tokens(eng.device, 0), non_blocking=True)
+            host[1:n + 1].copy_(out[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.h2d_bytes = g.builder.last_h2d_bytes
-        self.d2h_bytes = n * 4
+        self.d2h_bytes = (n + 1) * 4
         return _StepInFlight(self._launched, list(slots), host, ev)
 
     @property
     def _hosts(self):
         h = self.__dict__.get("_host_pair")
         if h is None:
-            h = self.__dict__["_host_pair"] = [torch.empty(1024, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            h = self.__dict__["_host_pair"] = [torch.empty(1025, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         return h
 
-    def _wait(self, step: _StepInFlight) -> list[int]:
+    def _wait(self, step: _StepInFlight, check: bool = True) -> list[int]:
+        """The step's tokens, once it has finished.  The status word came with them: a kernel that
+        gave up on a bounded wait in this step raises KernelError here (`check`)."""
         step.event.synchronize()
-        toks = step.host[:len(step.slots)].tolist()
+        vals = step.host[:len(step.slots) + 1].tolist()
+        toks = vals[1:]
         still = []
         for number, slots in self._held:
             if number <= step.number:
@@ -258,13 +290,25 @@ class GraphBackend(EngineBackend):
             else:
                 still.append((number, slots))
         self._held = still
+        if check:
+            kernels.raise_on_status(vals[0], self.engine.device)
         return toks
 
-    def _drain(self) -> None:
+    def _drain(self, check: bool = True) -> None:
         if self._ahead is not None:
-            self._wait(self._ahead)
-            self._ahead = None
+            step, self._ahead = self._ahead, None
+            self._wait(step, check)
         self._fed = {}
+
+    def abort(self, slots):
+        """After a failed step: waits for what is in flight, then gives back `slots` and whatever
+        was held until a step ahead had finished."""
+        self._drain(check=False)
+        torch.cuda.synchronize(self.engine.device)
+        for _, held in self._held:
+            self.engine.release(held)
+        self._held = []
+        self.engine.release([s for s in slots if self.engine.cache.slots.holds(s)])
 
     def start(self, prompts, u01, histories):
         self._drain()

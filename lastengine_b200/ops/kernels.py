@@ -67,6 +67,7 @@ def _declare(L) -> None:
         "leb_gemm_bf16_skinny": [P, I, P, P, I, I, I, I, I, I, P, I, P, I, I, F, P, P, P, P, P],
         "leb_gemm_bf16_tc_supported": [P, P, I, I],
         "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
+        "leb_selftest_bounded_wait": [P, I, I, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -74,6 +75,8 @@ def _declare(L) -> None:
         fn.restype = c_int
     L.leb_launch_count.restype = ctypes.c_longlong
     L.leb_launch_count.argtypes = []
+    L.leb_sm_count.restype = c_int
+    L.leb_sm_count.argtypes = []
     for name, args in _OPTIONAL.items():
         fn = getattr(L, name, None)
         if fn is not None:
@@ -264,7 +267,19 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
         _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, _stream()))
 
 
-def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """SMs of the current device, asked once per device."""
+    d = torch.cuda.current_device()
+    n = _sm_counts.get(d)
+    if n is None:
+        n = _sm_counts[d] = max(1, int(lib().leb_sm_count()))
+    return n
+
+
+def attention_splits(batch, nkv: int, G: int, sm_count: int | None = None) -> int:
     """How many blocks share one sequence's key range in a decode step (1 for prompts).
 
     Measured on B200 (head size 64, 8 kv heads): about 1024 positions per block is best with many
@@ -276,6 +291,8 @@ def attention_splits(batch, nkv: int, G: int, sm_count: int = 148) -> int:
     """
     if batch.max_qlen != 1:
         return 1
+    if sm_count is None:
+        sm_count = globals()["sm_count"]()
     kv = max(int(batch.max_kvlen), 1)
     per = max(batch.n_seqs * nkv * ((G + 15) // 16), 1)
     best, best_cost = 1, None
@@ -379,8 +396,23 @@ class SplitNorm:
         self.filled = False      # set by the product that wrote values and ssq
 
 
-def split_norm_ok(M: int, dtype: torch.dtype) -> bool:
-    return dtype == torch.bfloat16 and 0 < M <= SKINNY_M
+def split_norm_ok(M: int, dtype: torch.dtype, reader_weight: torch.Tensor | None = None) -> bool:
+    """Whether a step of M rows may split a norm in front of a product with `reader_weight`
+    [N, K].  Once the norm is split its input exists only as bfloat16(x * g), so the product that
+    reads it must be one that can scale its rows: the weight stream (up to SMALL_M rows) or the
+    sliced tcgen05 product (up to SKINNY_M rows, N below its limit, operands TMA can fetch).  A
+    reader that does not say what it multiplies with gets the split only where the weight stream
+    runs."""
+    if dtype != torch.bfloat16 or not 0 < M <= SKINNY_M:
+        return False
+    if reader_weight is None:
+        return M <= SMALL_M
+    if reader_weight.dim() != 2 or reader_weight.dtype != torch.bfloat16:
+        return False
+    N, K = reader_weight.shape
+    if K % 8 != 0 or reader_weight.data_ptr() % 16 != 0:
+        return False
+    return M <= SMALL_M or N < SKINNY_MAX_N
 
 
 def _scale_args(scale: "SplitNorm | None", M: int, K: int):
@@ -449,7 +481,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
         return
     # few dozen rows: W as the wide operand with K sliced over blocks, unless N alone already gives
     # every SM several tiles (the output head), where the persistent kernel streams W better
-    if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < 128 * 296
+    if (not streaming and group_offsets is None and SMALL_M < M <= SKINNY_M and N < SKINNY_MAX_N
             and linear_skinny(out, x, w, epilogue, norm_args=(ssq, parts, d_in, eps, ev, eg, es))):
         if ev is not None:
             emit.filled = True
@@ -593,24 +625,60 @@ def launch_count() -> int:
 
 
 # ---- the tcgen05 matrix product ----------------------------------------------------------------
+# The status word of a device sits right in front of the buffer the chosen tokens of a step go
+# to, so that the copy that brings the tokens to the host brings the word along.
+RESULT_TOKENS = 8192      # chosen tokens the shared buffer holds; larger steps use a buffer of their own
+_STATUS_AT = 3            # the tokens then start on a 16-byte boundary
+_tc_block: dict[int, torch.Tensor] = {}
 _tc_status: dict[int, torch.Tensor] = {}
 
 
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def _status_block(device: torch.device) -> torch.Tensor:
+    i = _device_index(device)
+    if i not in _tc_block:
+        _tc_block[i] = torch.zeros(_STATUS_AT + 1 + RESULT_TOKENS, dtype=torch.int32, device=device)
+        _tc_status[i] = _tc_block[i][_STATUS_AT:_STATUS_AT + 1]
+    return _tc_block[i]
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
-    i = device.index if device.index is not None else torch.cuda.current_device()
-    if i not in _tc_status:
-        _tc_status[i] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tc_status[i]
+    _status_block(device)
+    return _tc_status[_device_index(device)]
+
+
+def result_tokens(device: torch.device) -> torch.Tensor:
+    """int32 [RESULT_TOKENS] for a step's chosen tokens, directly behind the device's status word."""
+    return _status_block(device)[_STATUS_AT + 1:]
+
+
+def status_and_tokens(device: torch.device, n: int) -> torch.Tensor:
+    """The status word followed by the first n chosen tokens: what one copy brings to the host."""
+    return _status_block(device)[_STATUS_AT:_STATUS_AT + 1 + n]
+
+
+def raise_on_status(value: int, device: torch.device) -> None:
+    """`value`: the status word as the host read it.  Non-zero: a kernel gave up on a bounded wait
+    and what the step computed is not valid; the word is cleared and KernelError raised."""
+    if value != 0:
+        _status_word(device).zero_()
+        raise KernelError(f"a tensor-core kernel gave up waiting (role {value}) on cuda:{_device_index(device)}; "
+                          "the step's result is not valid")
 
 
 def check_device_status() -> None:
     """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
     for i, t in _tc_status.items():
-        v = int(t.item())
-        if v != 0:
-            t.zero_()
-            raise KernelError(f"a tensor-core matrix product gave up waiting (role {v}) on cuda:{i}; "
-                              "its result is not valid")
+        raise_on_status(int(t.item()), t.device)
+
+
+def selftest_bounded_wait(device: torch.device, limit: int = 2000, role: int = 9) -> None:
+    """Launches one block that waits, with the kernels' own bounded wait, on a barrier nobody
+    arrives on; it gives up after `limit` polls and sets the device's status word to `role`."""
+    _check(lib().leb_selftest_bounded_wait(_ptr(_status_word(device)), int(limit), int(role), _stream()))
 
 
 def _tma_ok(x: torch.Tensor, w: torch.Tensor, K: int) -> bool:
@@ -646,6 +714,7 @@ def linear_tc2(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: in
 
 
 SKINNY_M = 128   # rows up to which W is the wide tcgen05 operand and K is sliced over blocks
+SKINNY_MAX_N = 128 * 296   # from here on N alone gives every SM several tiles and the persistent kernel streams W better
 _skinny_ws: dict[int, list[torch.Tensor]] = {}
 
 

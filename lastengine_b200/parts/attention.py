@@ -74,6 +74,9 @@ class AttentionMixer(Mixer):
             self.k_norm_w = tensors["k_layernorm.weight"].contiguous() if self.own_kv else None
         self.position.load({n[len("position."):]: v for n, v in tensors.items() if n.startswith("position.")}, env)
 
+    def split_reader_weight(self):
+        return self.w_in
+
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         nh, nkv, hd = self.nh, self.nkv, self.hd
         M = h.shape[0]
@@ -109,13 +112,16 @@ class AttentionMixer(Mixer):
             qn = ws.get("attn.qn", (M, nh * hd), env.dtype)
             kernels.qk_rope_store(qn, q_in, None, None, None, None, cache.block_table, batch, self.q_norm_w, None,
                                   self.eps, None, 0, True, nh, nkv, hd, cache.page_size)
-            kn = None
+            kn = vn = None
             if writes:
                 kn = ws.get("attn.kn", (M, nkv * hd), env.dtype)
                 kernels.qk_rope_store(kn, k_in, None, None, None, None, cache.block_table, batch, self.k_norm_w, None,
                                       self.eps, None, 0, True, nkv, nkv, hd, cache.page_size)
+                vn = ws.get("attn.vn", (M, nkv * hd), env.dtype)      # the values beside them, rows as wide as kn's
+                kernels.qk_rope_store(vn, v_in, None, None, None, None, cache.block_table, batch, None, None,
+                                      self.eps, None, 0, True, nkv, nkv, hd, cache.page_size)
             self.position.apply(qn.view(M, nh, hd), kn.view(M, nkv, hd) if writes else None, batch.row_pos)
-            kernels.qk_rope_store(q, qn, kn, v_in, kp, vp, cache.block_table, batch, None, None, self.eps,
+            kernels.qk_rope_store(q, qn, kn, vn, kp, vp, cache.block_table, batch, None, None, self.eps,
                                   None, 0, True, nh, nkv, hd, cache.page_size)
         o = ws.get("attn.o", (M, nh * hd), env.dtype)
         n_splits = kernels.attention_splits(batch, nkv, nh // nkv)

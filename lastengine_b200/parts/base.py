@@ -161,6 +161,12 @@ class BuildEnv:
 class Part:
     split_norm = False     # True: forward() honours env.split_in / env.split_out (see BuildEnv)
 
+    def split_reader_weight(self):
+        """For parts with `split_norm`: the weight [N, K] of the product that reads the part's input
+        (the one that gets `scale=`), so that a block offers a split only where that product can
+        take it.  None: the block offers it only for steps the weight stream runs."""
+        return None
+
     def tensors(self) -> dict[str, TensorSpec]:
         return {}
 

@@ -16,7 +16,6 @@ import torch
 
 from ..ops import kernels
 from ..registry import BLOCKS
-from .norm import RMSNorm
 
 
 @BLOCKS.register("pre_norm_residual")
@@ -42,9 +41,12 @@ class PreNormResidualBlock:
         """Before `producer` adds into x: if `norm` (the next reader of x) can be split between it
         and `consumer`, asks the producer to leave its half.  Returns the split or None."""
         M, D = x.shape
-        if not (type(norm) is RMSNorm and getattr(producer, "split_norm", False)
-                and getattr(consumer, "split_norm", False) and kernels.split_norm_ok(M, env.dtype)):
+        if not (getattr(norm, "splittable", False) and getattr(producer, "split_norm", False)
+                and getattr(consumer, "split_norm", False)):
             return None
+        reader = getattr(consumer, "split_reader_weight", None)
+        if not kernels.split_norm_ok(M, env.dtype, reader() if callable(reader) else None):
+            return None      # the product that would read the split's values could not scale its rows
         ws = env.workspace
         sp = kernels.SplitNorm(ws.get(f"block.split.values{which}", (M, D), torch.bfloat16),
                                ws.get(f"block.split.ssq{which}", (M, -(-D // 16)), torch.float32),

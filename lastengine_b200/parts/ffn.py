@@ -50,6 +50,9 @@ class SwiGLU(FeedForward):
         self.w13 = fuse_gate_up(tensors["w1.weight"], tensors["w3.weight"], self.fused)
         self.w2 = tensors["w2.weight"].contiguous()
 
+    def split_reader_weight(self):
+        return self.w13
+
     def forward(self, h, out, accumulate, batch, env) -> None:
         M = h.shape[0]
         ws = env.workspace

@@ -10,6 +10,10 @@ from .base import NORM, BuildEnv, Part, TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Part):
+    # y = x * r * w with one factor r per row: a block may leave bfloat16(x * w) to the product
+    # before it and r to the product after it (a norm with a mean or a bias could not be split so)
+    splittable = True
+
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)

@@ -44,6 +44,9 @@ class ShortConvMixer(Mixer):
         self.w_out = tensors["out_proj.weight"].contiguous()
         self.b_conv = tensors["conv.bias"].contiguous() if self.bias else None
 
+    def split_reader_weight(self):
+        return self.w_in
+
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         M = h.shape[0]
         ws = env.workspace

@@ -185,6 +185,19 @@ def test_kept_dtypes():
     assert kept_dtype(TensorSpec((1,), MATRIX), torch.int64, bf) == torch.int32
 
 
+def test_engine_options():
+    from lastengine_b200 import EngineOptions
+    o = EngineOptions.of(None, dtype=torch.float32, max_tokens=100)
+    assert o.dtype == "float32" and o.max_tokens == 100 and o.max_batch_tokens == 16384 and o.use_graphs
+    assert EngineOptions.of(o, max_seqs=3).max_tokens == 100
+    with pytest.raises(TypeError, match="max_token"):
+        EngineOptions.of(None, max_token=5)
+    with pytest.raises(ValueError):
+        EngineOptions(dtype="float16")
+    with pytest.raises(ValueError):
+        EngineOptions(max_tokens=0)
+
+
 def test_engine_refuses_to_run_without_cuda():
     if torch.cuda.is_available():
         pytest.skip("a GPU is present")

@@ -221,6 +221,61 @@ def test_toy_parts_register_build_and_step():
         ARCHITECTURES.unregister("ToyForCausalLM")
 
 
+def test_toy_position_encoding_defined_here():
+    """A position encoding that is no rotation, defined in this test and registered: it adds a
+    feature of the position, log(1 + pos) / 8, to the first element of every normed query and key
+    head.  The attention mixer is built with it by name and knows nothing of it; a prompt in three
+    pieces must give the plain computation with the same encoding."""
+    from lastengine_b200.cache import CacheView
+    from lastengine_b200.parts.attention import AttentionMixer
+    from lastengine_b200.parts.base import PartSpec, PositionEncoding
+    from lastengine_b200.registry import POSITION_ENCODINGS
+
+    @POSITION_ENCODINGS.register("toy_log_position", replace=True)
+    class LogPosition(PositionEncoding):
+        def __init__(self, strength):
+            self.strength = strength
+
+        def apply(self, q, k, row_pos):
+            f = (torch.log1p(row_pos.float()) * self.strength).to(q.dtype)[:, None]
+            q[:, :, 0] += f
+            if k is not None:
+                k[:, :, 0] += f
+
+    def plain_encoding(v, positions, rope_dim, theta, neox=True, freq_factors=None):
+        out = v.clone()
+        out[:, :, 0] += torch.log1p(positions.to(v.dtype))[:, None] * 0.125
+        return out
+
+    try:
+        for dtype, rnd, tol in CASES:
+            env = env_for(dtype)
+            nh, nkv, hd, D = 4, 2, 32, 64
+            part = AttentionMixer(hidden_size=D, num_heads=nh, num_kv_heads=nkv, head_dim=hd, norm_eps=1e-5,
+                                  position=PartSpec("toy_log_position", {"strength": 0.125}))
+            assert part.position.fused_rotary() is None
+            w = load_part(part, env, 410)
+            T = 90
+            h = rnd(gen(T, D, seed=6).double())
+            pool = torch.zeros(2, 4, nkv, 64, hd, device=DEV, dtype=dtype)
+            table = np.array([[1, 3]], dtype=np.int32)
+            out = torch.zeros(T, D, device=DEV)
+            hdv = h.to(device=DEV, dtype=dtype)
+            for lo, hi in ((0, 50), (50, 51), (51, 90)):
+                b = one_sequence_batch(hi - lo, lo, table=table)
+                view = CacheView(writable=True, k=pool[0], v=pool[1].view(4, nkv, hd, 64), block_table=b.tables[0])
+                part.forward(hdv[lo:hi], out[lo:hi], False, b, view, env)
+            orig = P.rope
+            P.rope = plain_encoding
+            try:
+                want = P.attention(h, w, T, nh=nh, nkv=nkv, hd=hd, eps=1e-5, theta=0.0, rope_dim=hd, rnd=rnd)
+            finally:
+                P.rope = orig
+            assert err(out, want) < tol
+    finally:
+        POSITION_ENCODINGS.unregister("toy_log_position")
+
+
 def test_toy_part_takes_part_in_split_norms():
     """A feed-forward defined here that says `split_norm = True` and passes the two halves on to its
     products: in decode steps the block then splits the norms around it (no norm kernel between
