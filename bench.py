@@ -16,7 +16,12 @@ A step is one decode step of the whole batch.  One JSON line goes to stdout:
   prefill    one prompt of 2,048 tokens: tokens/s, and the fraction of the bf16 peak
   roofline   the bytes a decode step must read (every weight once, the cache of the live
              sequences) over its time, against the measured copy bandwidth
-  points     decode tokens/s at batch 1 and 64, same context
+  points     decode tokens/s at batch 1 and 64, same context; and the scenario of 512-token
+             prompts followed by 256 decode steps (context 512 to 768) at batch 1, 8 and 64, each with
+             its milliseconds per step and its fraction of the copy bandwidth (p512_*)
+  roofline.kernels   the kernels a decode step and the prompt spend most of their time in, each timed
+             with CUDA events around its launches (one kernel after the other, outside the timed
+             runs) against the bytes or flops it has to move
 
 Weights (1.8 GB) are far larger than L2, so consecutive steps cannot be served from L2.
 """
@@ -61,6 +66,9 @@ MODELS = {"1.2b": ("LFM2-1.2B-shaped LFM3 hybrid", CONFIG_1P2B), "2.6b": ("LFM2-
           "8b-a1b": ("LFM2-8B-A1B-shaped LFM3 hybrid MoE", CONFIG_8B_A1B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+P512_PROMPT, P512_STEPS = 512, 256      # the decode scenario the reference's numbers are defined on
+E2E_MIN_STEPS = 256                     # the end-to-end run never has fewer decode steps than this
+E2E_FIRST_STEPS = 32                    # ... and says separately how the first ones after the prompts went
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -117,42 +125,20 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
-def model_numbers(eng, cfg: dict) -> dict:
-    """Bytes and flops of a step, from the model's own tensors."""
-    import torch
-    from lastengine_b200.config import Lfm3Config
-    c = Lfm3Config.from_dict(cfg)
-    wbytes = eng.weight_bytes()
-    n_attn = len(c.attention_layers)
-    kv_bytes_per_token = n_attn * 2 * c.num_key_value_heads * c.head_dim * (2 if eng.dtype == torch.bfloat16 else 4)
-    state_bytes_per_seq = len(c.conv_layers) * c.hidden_size * (c.conv_L_cache - 1) * 4
-    D, F, V = c.hidden_size, c.ffn_dim, c.vocab_size
-    E, k, Fe = c.num_experts, c.num_experts_per_tok, c.moe_intermediate_size
-    per_tok, expert_bytes = 0, 0
-    for li, kind in enumerate(c.layer_types):
-        if kind == "conv":
-            per_tok += 2 * D * 3 * D + 2 * D * D
-        else:
-            per_tok += 2 * D * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim + 2 * c.num_attention_heads * c.head_dim * D
-        if E > 0 and li >= c.num_dense_layers:
-            per_tok += 2 * D * E + k * (2 * D * 2 * Fe + 2 * Fe * D)
-            expert_bytes += E * 3 * Fe * D * 2
-        else:
-            per_tok += 2 * D * 2 * F + 2 * F * D
-    return {"weight_bytes": wbytes, "kv_bytes_per_token": kv_bytes_per_token, "state_bytes_per_seq": state_bytes_per_seq,
-            "linear_flops_per_token": per_tok, "head_flops_per_row": 2 * D * V,
-            "attn_flops_per_qk": 4 * c.num_attention_heads * c.head_dim * n_attn,
-            "expert_bytes": expert_bytes, "experts": E, "experts_per_token": k}
+def model_numbers(eng) -> dict:
+    """Bytes and flops of a step, from what the engine's parts say of themselves."""
+    c = eng.step_costs()
+    return {"weight_bytes": eng.weight_bytes(), "kv_bytes_per_token": c["kv_bytes_per_token"],
+            "state_bytes_per_seq": c["state_bytes_per_seq"], "linear_flops_per_token": c["layer_flops_per_row"],
+            "head_flops_per_row": c["head_flops_per_row"], "attn_flops_per_qk": c["flops_per_query_key"]}
 
 
-def used_weight_bytes(nums: dict, batch: int) -> float:
-    """The weights a decode step of `batch` rows reads: all of a dense model; of the experts the
-    share that `batch` rows with uniform routing are expected to choose."""
-    E, k = nums["experts"], nums["experts_per_token"]
-    if E <= 0:
-        return float(nums["weight_bytes"])
-    share = 1.0 - (1.0 - k / E) ** batch
-    return nums["weight_bytes"] - nums["expert_bytes"] * (1.0 - share)
+def decode_step_bytes(eng, nums: dict, batch: int, avg_context: float) -> float:
+    """What a decode step has to read: every weight it uses once (of experts the share that `batch`
+    rows are expected to choose), the cache of the live sequences, and their fixed-size state (read
+    and written)."""
+    return (eng.weight_bytes_read(batch) + batch * avg_context * nums["kv_bytes_per_token"]
+            + 2 * batch * nums["state_bytes_per_seq"])
 
 
 def time_prefill(eng, n_tokens: int, warmup: int, reps: int, rng) -> float:
@@ -223,18 +209,82 @@ def time_decode(eng, batch: int, context: int, steps: int, warmup: int, rng, clo
 
 
 def time_e2e(eng, batch: int, context: int, steps: int, rng) -> dict:
-    """The same decode through Engine.generate: host ids in, host ids out, every step."""
+    """The same decode through Engine.generate: host ids in, host ids out, every step.  `value` is
+    over all `steps` decode steps of one call; `first_steps_value` over the first E2E_FIRST_STEPS of
+    a call of its own (right after the prompts the device runs at its power cap for some tens of
+    milliseconds, which a short run shows and a long one averages out)."""
     from lastengine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
     prompts = [rng.integers(0, eng.vocab_size, size=context - steps - 1).tolist() for _ in range(batch)]
-    # a short call first: it captures the decode graph of this batch size, as a server's first request would
-    eng.generate([p[:64] for p in prompts], SamplingParams(temperature=0.0), max_new_tokens=4, stop_token_ids=[],
-                 max_batch=batch, max_seq_len=context + 1)
-    res = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=steps + 1, stop_token_ids=[],
-                       max_batch=batch, max_seq_len=context + 1)
+    # short calls first: they capture the decode graphs of this batch size, as a server's first requests would
+    eng.generate([p[:64] for p in prompts], greedy, max_new_tokens=4, stop_token_ids=[], max_batch=batch, max_seq_len=context + 1)
+    eng.generate(prompts, greedy, max_new_tokens=4, stop_token_ids=[], max_batch=batch, max_seq_len=context + 1)
+    first = eng.generate(prompts, greedy, max_new_tokens=E2E_FIRST_STEPS + 1, stop_token_ids=[], max_batch=batch,
+                         max_seq_len=context + 1).stats
+    res = eng.generate(prompts, greedy, max_new_tokens=steps + 1, stop_token_ids=[], max_batch=batch, max_seq_len=context + 1)
     st = res.stats
     return {"value": st.decode_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": res.backend.h2d_bytes,
             "d2h_bytes_per_step": res.backend.d2h_bytes, "decode_steps": st.decode_steps,
+            "first_steps": first.decode_steps, "first_steps_value": first.decode_tok_s,
             "prefill_tok_s": st.prefill_tok_s}
+
+
+# kernel entry points by what they do, for roofline.kernels
+KERNEL_CLASSES = {
+    "leb_gemm_bf16_stream": "weight-streaming products", "leb_gemm_bf16_stream_conv": "weight-streaming products",
+    "leb_gemm_bf16_stream_grouped": "weight-streaming products", "leb_gemm_bf16_skinny": "weight-streaming products",
+    "leb_gemm_bf16_small": "weight-streaming products",
+    "leb_attention_decode": "decode attention", "leb_attention_merge": "decode attention",
+    "leb_gemm_bf16_tc": "tcgen05 products", "leb_gemm_bf16_tc2": "tcgen05 products", "leb_gemm_bf16_tc_grouped": "tcgen05 products",
+    "leb_attention_prefill_tc": "tcgen05 prompt attention", "leb_attention_prefill": "prompt attention",
+}
+
+
+def time_kernels(eng, nums: dict, batch: int, context: int, pk: dict, rng) -> list[dict]:
+    """One decode step of `batch` sequences at `context` and one prompt of PREFILL_TOKENS under the
+    per-kernel event timer (launched one by one, no graph): for the kernel classes that take most of
+    each, the time of their launches against the bytes (decode) or flops (prompt) they have to move."""
+    import torch
+    from lastengine_b200.ops import kernels
+    out = []
+    seqs = fill_context(eng, batch, context - 2, rng)
+    eng.step(seqs, [[1]] * batch, "last")                      # warm: kernels loaded, scratch sized
+    torch.cuda.synchronize()
+    with kernels.KernelTimer(head_start_ms=5.0) as t:
+        eng.step(seqs, [[2]] * batch, "last")
+    eng.release(seqs)
+    work = {"weight-streaming products": eng.weight_bytes_read(batch),
+            "decode attention": batch * context * nums["kv_bytes_per_token"]}
+    out += _classes(t.summary(), work, "GB/s", 1e9, pk["hbm_gbs"], f"decode step, batch {batch}, context {context}")
+    toks = rng.integers(0, eng.vocab_size, size=PREFILL_TOKENS).tolist()
+    s = eng.new_sequence()
+    eng.step([s], [toks], "last")
+    eng.release(s)
+    s = eng.new_sequence()
+    torch.cuda.synchronize()
+    with kernels.KernelTimer(head_start_ms=5.0) as t:
+        eng.step([s], [toks], "last")
+    eng.release(s)
+    work = {"tcgen05 products": PREFILL_TOKENS * nums["linear_flops_per_token"],
+            "tcgen05 prompt attention": nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2}
+    out += _classes(t.summary(), work, "TFLOP/s", 1e12, pk["bf16_tflops"], f"prompt of {PREFILL_TOKENS} tokens")
+    return out
+
+
+def _classes(summary: dict, work: dict, unit: str, per: float, peak: float, where: str) -> list[dict]:
+    acc: dict[str, list] = {}
+    total = sum(ms for _, ms in summary.values())
+    for name, (calls, ms) in summary.items():
+        e = acc.setdefault(KERNEL_CLASSES.get(name, name), [0, 0.0])
+        e[0] += calls
+        e[1] += ms
+    rows = []
+    for cls, (calls, ms) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:3]:
+        row = {"where": where, "kernels": cls, "launches": calls, "ms": ms, "share_of_kernel_time": ms / total if total else 0.0}
+        if cls in work and ms > 0:
+            row.update({"achieved": work[cls] / (ms / 1e3) / per, "unit": unit, "frac": work[cls] / (ms / 1e3) / per / peak})
+        rows.append(row)
+    return rows
 
 
 def main() -> int:
@@ -249,6 +299,7 @@ def main() -> int:
     ap.add_argument("--model", default="1.2b", choices=sorted(MODELS), help="shape to run (default: the 1.2B shape the headline is quoted on)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--no-per-kernel", action="store_true", help="leave out roofline.kernels (the per-kernel event timing)")
     ap.add_argument("--only-prefill", action="store_true", help="time the prompt step only (for profiling)")
     ap.add_argument("--only-decode", action="store_true", help="skip the prompt timing (for profiling)")
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
@@ -284,7 +335,7 @@ def main() -> int:
     t0 = time.time()
     eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_b * (args.context + 64) + 4096,
                              max_seqs=max_b + 8)
-    nums = model_numbers(eng, cfg)
+    nums = model_numbers(eng)
     from lastengine_b200.config import Lfm3Config
     tc = Lfm3Config.from_dict(cfg)
     print(f"[bench] model ready in {time.time() - t0:.1f}s: {nums['weight_bytes'] / 1e9:.3f} GB of weights", file=sys.stderr)
@@ -324,8 +375,7 @@ def main() -> int:
     launches0 = kernels.launch_count()
     main_run = time_decode(eng, args.batch, args.context, args.steps, args.warmup, rng, clocks)
     launches = main_run["launches_per_step"] * args.steps
-    step_bytes = (used_weight_bytes(nums, args.batch) + args.batch * main_run["avg_context"] * nums["kv_bytes_per_token"]
-                  + 2 * args.batch * nums["state_bytes_per_seq"])
+    step_bytes = decode_step_bytes(eng, nums, args.batch, main_run["avg_context"])
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
     clk = clocks.summary(*main_run["clock_rows"])
     print(f"[bench] decode b{args.batch}: {main_run['ms_per_step']:.4f} ms/step", file=sys.stderr)
@@ -335,11 +385,25 @@ def main() -> int:
             r = time_decode(eng, b, args.context, args.steps, args.warmup, rng)
             points[f"decode_b{b}"] = r["tok_s"]
             points[f"decode_b{b}_ms"] = r["ms_per_step"]
+            points[f"decode_b{b}_frac"] = decode_step_bytes(eng, nums, b, r["avg_context"]) / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
             print(f"[bench] decode b{b}: {r['ms_per_step']:.4f} ms/step", file=sys.stderr)
+        # the scenario the reference's numbers are defined on: prompts of 512 tokens, then 256 decode steps
+        for b in (1, 8, 64):
+            r = time_decode(eng, b, P512_PROMPT + P512_STEPS + args.warmup + 1, P512_STEPS, args.warmup, rng)
+            nbytes = decode_step_bytes(eng, nums, b, r["avg_context"])
+            points[f"p512_decode_b{b}"] = r["tok_s"]
+            points[f"p512_decode_b{b}_ms"] = r["ms_per_step"]
+            points[f"p512_decode_b{b}_gb"] = nbytes / 1e9
+            points[f"p512_decode_b{b}_frac"] = nbytes / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+            print(f"[bench] 512-token prompts, {P512_STEPS} steps, b{b}: {r['ms_per_step']:.4f} ms/step", file=sys.stderr)
     e2e = None
     if not args.skip_e2e:
-        e2e = time_e2e(eng, args.batch, args.context, args.steps, rng)
-        print(f"[bench] e2e b{args.batch}: {e2e['value']:.1f} tok/s", file=sys.stderr)
+        e2e = time_e2e(eng, args.batch, args.context, max(args.steps, E2E_MIN_STEPS), rng)
+        print(f"[bench] e2e b{args.batch}: {e2e['value']:.1f} tok/s over {e2e['decode_steps']} steps "
+              f"({e2e['first_steps_value']:.1f} over the first {E2E_FIRST_STEPS})", file=sys.stderr)
+    per_kernel = None
+    if not args.no_per_kernel:
+        per_kernel = time_kernels(eng, nums, args.batch, args.context, pk, rng)
     clocks.stop()
 
     line = {
@@ -357,7 +421,8 @@ def main() -> int:
                    "peaks": pk_src},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "of": pk_src, "bytes_per_step": step_bytes},
+                     "frac": achieved / pk["hbm_gbs"], "of": pk_src, "bytes_per_step": step_bytes,
+                     **({"kernels": per_kernel} if per_kernel else {})},
         "points": points,
         "gpu_launches": launches,
         "clocks": clk,

@@ -3,9 +3,10 @@
 A sequence gets a slot when it starts and gives it back when it ends; slots and pages are
 reused.  Layers are grouped by what they need:
 
-* a KV group per distinct (kv heads, head size, window): one pool of pages of `page_size`
-  positions, `[entry, K|V, page, kv_head, position in page, head_dim]`, with a page pool and a
-  page list per sequence of its own.  A windowed group gives pages back once every position in
+* a KV group per distinct (kv heads, key head size, value head size, window): pools of pages of
+  `page_size` positions, keys `[entry, page, kv_head, position in page, head_dim]` and values
+  `[entry, page, kv_head, value_dim, position in page]`, with a page pool and a page list per
+  sequence of its own.  A windowed group gives pages back once every position in
   them has left the window.
 * a state group per distinct (shape, dtype): `[entry, slot, *shape]`, zeroed when a slot is
   given out (the reference zeroes its convolution state on reset, src/gpu/dense.rs:264-267).
@@ -35,7 +36,7 @@ class CacheView:
     writable: bool
     page_size: int = PAGE_SIZE
     k: torch.Tensor | None = None            # [page, kv_head, page_size, head_dim]
-    v: torch.Tensor | None = None            # [page, kv_head, head_dim, page_size] (positions contiguous)
+    v: torch.Tensor | None = None            # [page, kv_head, value_dim, page_size] (positions contiguous)
     block_table: torch.Tensor | None = None  # int32 [sequences of the step, pages]
     state: torch.Tensor | None = None        # [slot, *shape]
 
@@ -46,9 +47,11 @@ class KVGroup:
         self.spec, self.entries = spec, list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.page_size = page_size
-        # keys as [.., position, dim]; the value half is used as [.., dim, position] (same size)
-        self.pool = torch.zeros((len(entries), 2, n_pages, spec.n_kv_heads, page_size, spec.head_dim),
-                                dtype=dtype, device=device)
+        # keys as [.., position, dim], values as [.., dim, position]
+        self.k_pool = torch.zeros((len(entries), n_pages, spec.n_kv_heads, page_size, spec.head_dim),
+                                  dtype=dtype, device=device)
+        self.v_pool = torch.zeros((len(entries), n_pages, spec.n_kv_heads, spec.value_dim, page_size),
+                                  dtype=dtype, device=device)
         self.pages = IdPool(n_pages, "cache page")
         self.seq_pages: dict[int, list[int]] = {}   # slot -> page of each page index (-1: given back)
 
@@ -183,7 +186,7 @@ class Cache:
             g = self.state_groups[gi]
             return int(np.prod(g.spec.shape, dtype=np.int64)) * g.data.element_size()
         sp = self.kv_groups[gi].spec
-        return 2 * length * sp.n_kv_heads * sp.head_dim * self.kv_groups[gi].pool.element_size()
+        return length * sp.n_kv_heads * (sp.head_dim + sp.value_dim) * self.kv_groups[gi].k_pool.element_size()
 
     def export_seq(self, slot: int) -> bytes:
         """What a sequence holds, as bytes: its length (u64, little-endian), then for every cache
@@ -205,11 +208,11 @@ class Cache:
             i, sp = g.index[entry], g.spec
             pages = g.seq_pages.get(slot, [])
             k = torch.zeros((len(pages) * ps, sp.n_kv_heads, sp.head_dim), dtype=self.dtype, device=self.device)
-            v = torch.zeros_like(k)
+            v = torch.zeros((len(pages) * ps, sp.n_kv_heads, sp.value_dim), dtype=self.dtype, device=self.device)
             for j, p in enumerate(pages):
                 if p >= 0:
-                    k[j * ps:(j + 1) * ps] = g.pool[i, 0, p].permute(1, 0, 2)
-                    v[j * ps:(j + 1) * ps] = g.pool[i, 1, p].view(sp.n_kv_heads, sp.head_dim, ps).permute(2, 0, 1)
+                    k[j * ps:(j + 1) * ps] = g.k_pool[i, p].permute(1, 0, 2)
+                    v[j * ps:(j + 1) * ps] = g.v_pool[i, p].permute(2, 0, 1)
             out.append(raw(k[:n].reshape(-1)))
             out.append(raw(v[:n].reshape(-1)))
         return b"".join(out)
@@ -245,18 +248,18 @@ class Cache:
             g = self.kv_groups[gi]
             i, sp = g.index[entry], g.spec
             pages = g.seq_pages.get(slot, [])
-            half = nb // 2
-            for which in (0, 1):
-                t = torch.zeros((len(pages) * ps, sp.n_kv_heads, sp.head_dim), dtype=self.dtype, device=self.device)
+            for which, width in ((0, sp.head_dim), (1, sp.value_dim)):
+                part = nb * width // (sp.head_dim + sp.value_dim)
+                t = torch.zeros((len(pages) * ps, sp.n_kv_heads, width), dtype=self.dtype, device=self.device)
                 if n:
-                    t[:n] = buf[o:o + half].clone().view(self.dtype).view(n, sp.n_kv_heads, sp.head_dim)
-                o += half
+                    t[:n] = buf[o:o + part].clone().view(self.dtype).view(n, sp.n_kv_heads, width)
+                o += part
                 for j, p in enumerate(pages):
                     rows = t[j * ps:(j + 1) * ps]
                     if which == 0:
-                        g.pool[i, 0, p] = rows.permute(1, 0, 2)
+                        g.k_pool[i, p] = rows.permute(1, 0, 2)
                     else:
-                        g.pool[i, 1, p].view(sp.n_kv_heads, sp.head_dim, ps).copy_(rows.permute(1, 2, 0))
+                        g.v_pool[i, p] = rows.permute(1, 2, 0)
         self.commit({slot: n})
         return slot
 
@@ -273,8 +276,7 @@ class Cache:
             g = self.kv_groups[gi]
             i = g.index[entry]
             sp = g.spec
-            return CacheView(writable=writable, page_size=self.page_size, k=g.pool[i, 0],
-                             v=g.pool[i, 1].view(-1, sp.n_kv_heads, sp.head_dim, self.page_size),
+            return CacheView(writable=writable, page_size=self.page_size, k=g.k_pool[i], v=g.v_pool[i],
                              block_table=tables[gi])
         g = self.state_groups[gi]
         return CacheView(writable=writable, page_size=self.page_size, state=g.data[g.index[entry]])
@@ -291,5 +293,5 @@ class Cache:
             assert set(g.seq_pages) <= self.slots._held, "a freed sequence still owns pages"
 
     def nbytes(self) -> int:
-        n = sum(g.pool.numel() * g.pool.element_size() for g in self.kv_groups)
+        n = sum((g.k_pool.numel() + g.v_pool.numel()) * g.k_pool.element_size() for g in self.kv_groups)
         return n + sum(g.data.numel() * g.data.element_size() for g in self.state_groups)

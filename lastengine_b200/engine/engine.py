@@ -284,6 +284,35 @@ class Engine:
         return out
 
     # ---- numbers for reports --------------------------------------------------------------
+    def step_costs(self) -> dict:
+        """What a step costs, summed over the schedule from what the parts say of themselves (no
+        knowledge of the architecture): matrix-product flops per row through the layers and per
+        row of logits, mixer flops per (row, cached position), cache bytes per position and state
+        bytes per sequence."""
+        esize = 2 if self.dtype == torch.bfloat16 else 4
+        layer_flops = pair_flops = kv_bytes = state_bytes = 0
+        for i, e in enumerate(self.plan.schedule):
+            blk = self.model.blocks[e.layer]
+            layer_flops += sum(p.flops_per_row() for p in blk.parts().values())
+            pair_flops += blk.mixer.flops_per_query_key()
+        for spec in self.model.cache_specs().values():
+            if spec is None:
+                continue
+            if hasattr(spec, "n_kv_heads"):
+                kv_bytes += spec.n_kv_heads * (spec.head_dim + spec.value_dim) * esize
+            else:
+                n = 1
+                for d in spec.shape:
+                    n *= int(d)
+                state_bytes += n * torch.empty((), dtype=spec.dtype).element_size()
+        return {"layer_flops_per_row": layer_flops, "head_flops_per_row": self.model.head.flops_per_row(),
+                "flops_per_query_key": pair_flops, "kv_bytes_per_token": kv_bytes, "state_bytes_per_seq": state_bytes}
+
+    def weight_bytes_read(self, rows: int) -> float:
+        """Bytes of weights a step of `rows` rows is expected to read: all of them, less the experts
+        that nobody is expected to choose."""
+        return self.weight_bytes() - sum(p.unread_weight_bytes(rows) for _, p in self.model.named_parts())
+
     def weight_bytes(self) -> int:
         seen, n = set(), 0
         for _, part in self.model.named_parts():

@@ -17,6 +17,7 @@ F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 _lib = None
+_timer = None      # a KernelTimer while one is active
 
 
 def lib():
@@ -24,7 +25,68 @@ def lib():
     if _lib is None:
         _lib = _build.load()
         _declare(_lib)
-    return _lib
+    return _lib if _timer is None else _timer.proxy
+
+
+class KernelTimer:
+    """Device time of every kernel entry point called while it is active, by name.
+
+        with kernels.KernelTimer() as t:
+            engine.step(...)
+        t.summary()  ->  {entry point: (calls, milliseconds)}, longest first
+
+    Every call is bracketed by two CUDA events on the launching stream, as the reference's per-kernel
+    timer does behind LE_EVT (src/gpu/dense.rs:47-51, :348-388).  An event between two kernels keeps
+    the second from starting under the first (programmatic dependent launch), so the times are
+    those of kernels run one after the other: they add up to more than the step takes, and their
+    shares are what to read.  `head_start_ms` > 0 first occupies the device for about that long, so
+    that the host has queued the step's launches before the device reaches them and no event pair
+    contains the host's time between two launches.  Not for captured graphs or timed runs."""
+
+    def __init__(self, head_start_ms: float = 0.0):
+        self.head_start_ms = float(head_start_ms)
+        self.events: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+        real = lib()
+        timer = self
+
+        class _Proxy:
+            def __getattr__(self, name):
+                fn = getattr(real, name)
+                if not name.startswith("leb_") or fn.argtypes is None or not fn.argtypes or fn.argtypes[-1] is not c_void_p:
+                    return fn          # queries and settings: no stream, nothing to time
+
+                def timed(*args):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    rc = fn(*args)
+                    b.record()
+                    timer.events.append((name, a, b))
+                    return rc
+                return timed
+        self.proxy = _Proxy()
+
+    def __enter__(self):
+        global _timer
+        if _timer is not None:
+            raise KernelError("a KernelTimer is already active")
+        if self.head_start_ms > 0:
+            torch.cuda._sleep(int(self.head_start_ms * 1.5e6))      # cycles, at some 1.5 GHz
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+        torch.cuda.synchronize()
+        return False
+
+    def summary(self) -> dict[str, tuple[int, float]]:
+        acc: dict[str, list] = {}
+        for name, a, b in self.events:
+            e = acc.setdefault(name, [0, 0.0])
+            e[0] += 1
+            e[1] += a.elapsed_time(b)
+        return {k: (v[0], v[1]) for k, v in sorted(acc.items(), key=lambda kv: -kv[1][1])}
 
 
 def _declare(L) -> None:

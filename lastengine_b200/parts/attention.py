@@ -77,6 +77,9 @@ class AttentionMixer(Mixer):
     def split_reader_weight(self):
         return self.w_in
 
+    def flops_per_query_key(self) -> int:
+        return 4 * self.nh * self.hd        # a score and a weighted value, a multiply-add each, per head and dimension
+
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         nh, nkv, hd = self.nh, self.nkv, self.hd
         M = h.shape[0]

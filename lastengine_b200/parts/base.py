@@ -56,10 +56,16 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Keys and values that grow with the sequence; `window` > 0 keeps only the last ones."""
+    """Keys and values that grow with the sequence; `window` > 0 keeps only the last ones.
+    `v_head_dim`: width of a value head where it differs from a key head's (None: the same)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -173,6 +179,22 @@ class Part:
     def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
         pass
 
+    # ---- what a row costs, for reports (a roofline needs no knowledge of the architecture) ----
+    def flops_per_row(self) -> int:
+        """Floating-point operations of one row through the part's matrix products (2 per multiply-add)."""
+        n = 0
+        for spec in self.tensors().values():
+            if spec.role == MATRIX:
+                k = 1
+                for d in spec.shape:
+                    k *= int(d)
+                n += 2 * k
+        return n
+
+    def unread_weight_bytes(self, rows: int) -> float:
+        """Bytes of the part's weights that a step of `rows` rows is expected NOT to read (experts nobody chose)."""
+        return 0.0
+
 
 class Mixer(Part):
     def cache_spec(self) -> KVSpec | StateSpec | None:
@@ -180,6 +202,10 @@ class Mixer(Part):
 
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         raise NotImplementedError
+
+    def flops_per_query_key(self) -> int:
+        """Operations per (query row, cached position) pair, for mixers that look back over the sequence."""
+        return 0
 
 
 class FeedForward(Part):

@@ -44,5 +44,8 @@ class LinearHead(Part):
     def tie(self, embedding: TokenEmbedding) -> None:
         self.weight = embedding.weight
 
+    def flops_per_row(self) -> int:
+        return 2 * self.V * self.D
+
     def forward(self, logits: torch.Tensor, xn: torch.Tensor) -> None:
         kernels.linear(logits, xn, self.weight)

@@ -101,6 +101,16 @@ class SigmoidTopKMoE(FeedForward):
                                              self.fused) for e in range(self.E)]).contiguous()
         self.w2 = torch.stack([tensors[f"experts.{e}.w2.weight"] for e in range(self.E)]).contiguous()
 
+    def flops_per_row(self) -> int:
+        return 2 * self.D * self.E + self.k * 6 * self.D * self.Fe       # the router, and k experts of three matrices
+
+    def unread_weight_bytes(self, rows: int) -> float:
+        """With uniform routing an expert is chosen by none of `rows` rows with probability (1 - k/E)^rows."""
+        if self.w13 is None:
+            return 0.0
+        per_expert = (self.w13[0].numel() + self.w2[0].numel()) * self.w13.element_size()
+        return self.E * per_expert * (1.0 - self.k / self.E) ** rows
+
     def forward(self, h, out, accumulate, batch, env) -> None:
         M = h.shape[0]
         P = M * self.k

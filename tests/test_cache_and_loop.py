@@ -30,7 +30,7 @@ def test_id_pool_never_loses_or_doubles():
 
 def make_cache(max_tokens=640, max_seqs=6):
     specs = {0: StateSpec((8, 2)), 1: KVSpec(2, 16), 2: StateSpec((8, 2)), 3: KVSpec(2, 16),
-             4: KVSpec(2, 16, window=100), 5: StateSpec((4,))}
+             4: KVSpec(2, 16, window=100, v_head_dim=24), 5: StateSpec((4,))}
     return Cache(specs, max_tokens=max_tokens, max_seqs=max_seqs, dtype=torch.float32, device="cpu")
 
 
@@ -39,7 +39,8 @@ def test_groups_have_storage_of_their_own():
     assert len(c.kv_groups) == 2 and len(c.state_groups) == 2
     full = c.kv_groups[c.group_of(1)[1]]
     win = c.kv_groups[c.group_of(4)[1]]
-    assert full.pool.shape == (2, 2, 10, 2, 64, 16) and win.pool.shape == (1, 2, 10, 2, 64, 16)
+    assert full.k_pool.shape == (2, 10, 2, 64, 16) and full.v_pool.shape == (2, 10, 2, 16, 64)
+    assert win.k_pool.shape == (1, 10, 2, 64, 16) and win.v_pool.shape == (1, 10, 2, 24, 64)      # values wider than keys
     assert c.state_groups[c.group_of(0)[1]].data.shape == (2, 6, 8, 2)
     assert c.group_of(1) == c.group_of(3) != c.group_of(4)
 
@@ -120,7 +121,8 @@ def test_a_sequence_goes_out_as_bytes_and_comes_back_in_other_pages():
     c = make_cache(max_tokens=1280, max_seqs=6)
     g = torch.Generator().manual_seed(3)
     for grp in c.kv_groups:
-        grp.pool.copy_(torch.randn(grp.pool.shape, generator=g))
+        grp.k_pool.copy_(torch.randn(grp.k_pool.shape, generator=g))
+        grp.v_pool.copy_(torch.randn(grp.v_pool.shape, generator=g))
     other = c.alloc_seq()
     c.reserve({other: 70}); c.commit({other: 70})          # so that the copy lands in other pages
     s = c.alloc_seq()
@@ -129,11 +131,15 @@ def test_a_sequence_goes_out_as_bytes_and_comes_back_in_other_pages():
     c.reserve({s: 150}); c.commit({s: 150})
     data = c.export_seq(s)
     kv = 2 * 150 * 2 * 16 * 4
-    assert len(data) == 8 + 3 * kv + (16 + 16 + 4) * 4 and int.from_bytes(data[:8], "little") == 150
+    kv_win = 150 * 2 * (16 + 24) * 4                        # the windowed entry's values are 24 wide
+    assert len(data) == 8 + 2 * kv + kv_win + (16 + 16 + 4) * 4 and int.from_bytes(data[:8], "little") == 150
     # keys of entry 1 follow the state of entry 0, as [position][kv head][dim]
     full = c.kv_groups[c.group_of(1)[1]]
     k = torch.frombuffer(bytearray(data[8 + 64:8 + 64 + kv // 2]), dtype=torch.float32).view(150, 2, 16)
-    assert torch.equal(k[70], full.pool[0, 0, full.seq_pages[s][1], :, 6, :])
+    assert torch.equal(k[70], full.k_pool[0, full.seq_pages[s][1], :, 6, :])
+    win = c.kv_groups[c.group_of(4)[1]]
+    v = torch.frombuffer(bytearray(data[-16 - kv_win + 150 * 2 * 16 * 4:-16]), dtype=torch.float32).view(150, 2, 24)
+    assert torch.equal(v[130], win.v_pool[0, win.seq_pages[s][2], :, :, 2])
     t = c.import_seq(data)
     assert t != s and c.length(t) == 150 and c.export_seq(t) == data
     assert set(full.seq_pages[t]).isdisjoint(full.seq_pages[s])

@@ -363,7 +363,7 @@ def test_layer_reads_another_layers_cache(tmp_path):
     load_random(eng.model, seed=9, norm_init="random")
     eng.loaded = True
     assert "layers.3.self_attn.k_proj.weight" not in eng.model.tensor_specs()
-    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].pool.shape[0] == 1
+    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].k_pool.shape[0] == 1
     toks = H.requests_for(TINY_A, [90], 6)[0]
     whole = H.run_whole(eng, toks)
     stepwise = H.run_tail(eng, toks, 40)

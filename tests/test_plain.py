@@ -144,3 +144,55 @@ def test_short_conv_against_the_references_own_kernels():
         out, st = P.short_conv(bcx, p, T, D=n, Lc=lc, state=st_in)
         assert torch.allclose(out, torch.from_numpy(g[f"y{case}"]).double(), atol=1e-5)
         assert torch.allclose(st.T, torch.from_numpy(g[f"state_out{case}"]).double(), atol=1e-6)
+
+
+def test_norm_swiglu_rotation_and_attention_against_the_references_own_kernels():
+    """tests/golden/dense_kernels_golden.npz holds inputs and outputs of the reference's `rmsnorm`,
+    `swiglu_gu`, `dn_prep` and `dn_attn` kernels, run unchanged on a GPU by
+    tests/golden/make_dense_kernels_golden.py.  The plain functions must reproduce them: eps inside
+    the root; silu(gate) * up over [gate | up] rows; the per-head norm before the rotation, both
+    pairings, a rotation over part of the head, frequency factors; in attention the kv head of a
+    query head, the scale, the window's first key, the head gate.  The reference keeps cached keys
+    and values in 16-bit floats and uses the fast exponential, hence 2e-3 for the attention chain."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dense_kernels_golden.npz"))
+    t64 = lambda name: torch.from_numpy(g[name]).double()
+    rel = lambda got, want: float((got - want).abs().max() / want.abs().max())
+    for case in range(3):
+        y = P.rms_norm(t64(f"norm_x{case}"), t64(f"norm_w{case}"), float(g[f"norm_eps{case}"]))
+        assert rel(y, t64(f"norm_y{case}")) < 1e-5
+    gu = t64("swiglu_gu")
+    ffn = gu.shape[1] // 2
+    assert rel(P.silu(gu[:, :ffn]) * gu[:, ffn:], t64("swiglu_y")) < 1e-5
+    n_prep = sum(1 for k in g.files if k.startswith("prep_x"))
+    assert n_prep == 5
+    for case in range(n_prep):
+        heads, hd, rd, neox, pos0, T = (int(v) for v in g[f"prep_meta{case}"])
+        x = t64(f"prep_x{case}")
+        if f"prep_nw{case}" in g.files:
+            x = P.rms_norm(x, t64(f"prep_nw{case}"), 1e-5)                  # the norm comes first
+        ff = t64(f"prep_ff{case}") if f"prep_ff{case}" in g.files else None
+        y = P.rope(x, torch.arange(pos0, pos0 + T), rd, float(g[f"prep_base{case}"]), neox=bool(neox), freq_factors=ff)
+        assert rel(y, t64(f"prep_y{case}")) < 2e-5, case     # float angles: positions up to 40 times base^0
+    n_attn = sum(1 for k in g.files if k.startswith("attn_o"))
+    assert n_attn == 5
+    for case in range(n_attn):
+        nh, nkv, hd, rd, win, T = (int(v) for v in g[f"attn_meta{case}"])
+        q, k, v = (t64(f"attn_{n}{case}").reshape(T, -1) for n in "qkv")
+        gate = t64(f"attn_gate{case}") if f"attn_gate{case}" in g.files else None
+        cols = [q, k, v] + ([gate] if gate is not None else [])
+        h = torch.cat(cols, dim=1)                                        # the projections only pick columns
+        D, o0 = h.shape[1], 0
+        p = {}
+        for name, width in (("q_proj", nh * hd), ("k_proj", nkv * hd), ("v_proj", nkv * hd), ("gate_proj", nh if gate is not None else 0)):
+            if width:
+                w = torch.zeros(width, D, dtype=torch.float64)
+                w[torch.arange(width), o0 + torch.arange(width)] = 1.0
+                p[f"{name}.weight"] = w
+                o0 += width
+        p["q_layernorm.weight"], p["k_layernorm.weight"] = t64(f"attn_qn{case}"), t64(f"attn_kn{case}")
+        p["out_proj.weight"] = torch.eye(nh * hd, dtype=torch.float64)
+        ff = t64(f"attn_ff{case}") if f"attn_ff{case}" in g.files else None
+        o = P.attention(h, p, T, nh=nh, nkv=nkv, hd=hd, eps=1e-5, theta=float(g[f"attn_base{case}"]), rope_dim=rd,
+                        window=win, gate=gate is not None, freq_factors=ff)
+        assert rel(o, t64(f"attn_o{case}").reshape(T, nh * hd)) < 2e-3, case
