@@ -68,6 +68,54 @@ __device__ __forceinline__ uint4 mask_positions(uint4 v, int first, int lo, int 
   return v;
 }
 
+// The step's per-head norm, rotation and cache write done here instead of in a kernel of their own
+// (all null: q is ready and the cache holds the new position already).  q_raw, k_raw and v_raw are
+// the projections of the step's rows (one per sequence) as the matrix product left them; every
+// block norms and rotates the query heads it needs, and the block whose key range ends with the
+// new position norms and rotates the new key, stores it and the new value in the cache, and only
+// then streams that range.  Same operations in the same order as qk_rope_store_lanes_kernel
+// (rope_cache.cu), so the two ways give the same bits.  Head sizes 64 and 128 with a split-half
+// rotation over the whole head.
+struct AtdPrep {
+  const bf16* q_raw;      // [rows, q_stride]
+  const bf16* k_raw;      // [rows, kv_stride] or null (the layer stores no keys)
+  const bf16* v_raw;
+  int q_stride, kv_stride;
+  bf16* k_store;          // the pools, writable
+  bf16* v_store;
+  const float* q_norm_w;  // [HD] or null
+  const float* k_norm_w;
+  const float* inv_freq;  // [HD / 2]
+  float eps;
+};
+
+// One head vector by one warp: norm over the head, split-half rotation, rounded to bfloat16.
+template <int HD>
+__device__ __forceinline__ void atd_prep_head(const bf16* __restrict__ src, const float* __restrict__ nw, float eps,
+                                              const float* cs, const float* sn, bf16* dst, int lane) {
+  constexpr int EPL = HD / 32, NP = EPL / 2;
+  float x[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; e++) x[e] = __bfloat162float(src[lane + 32 * e]);
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; e++) ss += x[e] * x[e];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int e = 0; e < EPL; e++) x[e] = x[e] * r * nw[lane + 32 * e];
+  }
+#pragma unroll
+  for (int p = 0; p < NP; p++) {
+    const float a = x[p], bb = x[p + NP];
+    x[p] = a * cs[p] - bb * sn[p];
+    x[p + NP] = a * sn[p] + bb * cs[p];
+  }
+#pragma unroll
+  for (int e = 0; e < EPL; e++) dst[lane + 32 * e] = __float2bfloat16_rn(x[e]);
+}
+
 template <int HD, int S>  // head_dim, a multiple of 32; stages of a warp's ring
 __global__ void __launch_bounds__(32 * ATD_WARPS)
 attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const bf16* __restrict__ q,
@@ -76,7 +124,7 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
                         const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
                         const int* __restrict__ seq_qstart, const bf16* __restrict__ gate,
                         int gate_stride, int nh, int nkv, int page_size, int window, float scale,
-                        int n_splits) {
+                        int n_splits, AtdPrep prep) {
   constexpr int KB = HD / 32;  // 32-wide pieces of head_dim
   constexpr int NT = HD / 8;   // 8-wide output tiles over head_dim
   constexpr int KBYTES = 32 * HD * 2, STAGE = 2 * KBYTES;   // keys, then values
@@ -90,7 +138,12 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
   float (*l_s)[16] = m_s + ATD_WARPS;
   static_assert(sizeof(float) * ATD_WARPS * 16 * (HD + 4 + 2) <= (size_t)ATD_WARPS * S * STAGE, "results must fit the rings");
 
-  pdl_wait();
+  // What follows up to pdl_wait() reads only what earlier steps left: the step's own tables (sent
+  // before its first kernel) and cache positions below the new one (written a step ago or more;
+  // a step starts with a copy or a graph launch, which orders it after everything before).  The
+  // kernel before this one made the step's q, k and v, and nothing here touches them or writes
+  // anything before the wait.
+  pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, c = lane & 3;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -101,9 +154,13 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
   // q, out and the partial results have one row per sequence of the launch (gridDim.y): a row
   // index beyond that (a seq_qstart taken from a step with several rows per sequence) is skipped
   // instead of being written past the end of those buffers
-  if (m_row >= gridDim.y) return;
+  if (m_row >= gridDim.y) {
+    pdl_wait();
+    return;
+  }
 
   if (slot < 0) {  // padding sequence
+    pdl_wait();
     for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
       int hh = idx / HD, d = idx % HD;
       if (n_splits == 1)
@@ -127,28 +184,6 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
   const int per_split = (n_blk + n_splits - 1) / n_splits;
   const int blk_lo = blk_first + split * per_split;
   const int blk_hi = min(blk_last + 1, blk_lo + per_split);
-
-  // Q fragments: heads r and r+8 of this kv head (zero beyond G)
-  uint4 qa[KB], qb[KB];
-  {
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    const bf16* qrow = q + (m_row * nh + h0) * HD;
-#pragma unroll
-    for (int j = 0; j < KB; j++) {
-      qa[j] = r < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + 32 * j + 8 * c) : zero;
-      qb[j] = r + 8 < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)(r + 8) * HD + 32 * j + 8 * c) : zero;
-    }
-  }
-
-  // scores are kept times log2(e), so that the exponentials are single exp2 steps
-  const float scale2 = scale * 1.4426950408889634f;
-  const bool upper = G > 8;   // rows 8..15 of the tiles hold heads at all
-  float mx[2] = {ATD_NEG, ATD_NEG}, l[2] = {0.f, 0.f};
-  float acc[NT][4];
-#pragma unroll
-  for (int n = 0; n < NT; n++)
-#pragma unroll
-    for (int e = 0; e < 4; e++) acc[n][e] = 0.f;
 
   const int* table = block_table + (size_t)b * bt_width;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(atd_smem) + warp * (S * STAGE);
@@ -177,8 +212,74 @@ attention_decode_kernel(bf16* __restrict__ out, float* __restrict__ part, const 
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  // The block of positions that holds the new one is written in this step (by the kernel before
+  // this one, or below): the first stages are asked for now unless one of them is that block.
+  const bool has_new = blk_lo <= blk_last && blk_last < blk_hi;
+  const bool early = !has_new || blk_last >= blk_lo + ATD_WARPS * (S - 1);
+  if (early) {
 #pragma unroll
-  for (int i = 0; i < S - 1; i++) issue();
+    for (int i = 0; i < S - 1; i++) issue();
+  }
+  pdl_wait();
+
+  // Q fragments: heads r and r+8 of this kv head (zero beyond G)
+  uint4 qa[KB], qb[KB];
+  const bf16* qrow = q + (m_row * nh + h0) * HD;
+  if constexpr (HD == 64 || HD == 128) {
+    if (prep.q_raw) {
+      __shared__ __align__(16) bf16 q_s[16 * HD];
+      constexpr int NP = HD / 64;
+      float cs[NP], sn[NP];
+#pragma unroll
+      for (int p = 0; p < NP; p++) {
+        const float th = (float)qpos * prep.inv_freq[lane + 32 * p];
+        cs[p] = cosf(th);
+        sn[p] = sinf(th);
+      }
+      for (int hh = warp; hh < G; hh += ATD_WARPS)
+        atd_prep_head<HD>(prep.q_raw + m_row * prep.q_stride + (size_t)(h0 + hh) * HD, prep.q_norm_w, prep.eps, cs, sn,
+                          q_s + hh * HD, lane);
+      // the new key and value: the block whose range holds the last block of positions stores them
+      // (before it asks for that block's copy, so that the copy finds them in the cache)
+      if (prep.k_raw && has_new) {
+        const int page = table[qpos / page_size], off = qpos % page_size;
+        if (page >= 0) {
+          if (warp == ATD_WARPS - 1)
+            atd_prep_head<HD>(prep.k_raw + m_row * prep.kv_stride + (size_t)kvh * HD, prep.k_norm_w, prep.eps, cs, sn,
+                              prep.k_store + (((size_t)page * nkv + kvh) * page_size + off) * HD, lane);
+          for (int d = threadIdx.x; d < HD; d += blockDim.x)
+            prep.v_store[(((size_t)page * nkv + kvh) * HD + d) * page_size + off] =
+                prep.v_raw[m_row * prep.kv_stride + (size_t)kvh * HD + d];
+        }
+        __threadfence();     // the copies read the cache through L2
+      }
+      __syncthreads();
+      qrow = q_s;
+    }
+  }
+  if (!early) {
+#pragma unroll
+    for (int i = 0; i < S - 1; i++) issue();
+  }
+  {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < KB; j++) {
+      qa[j] = r < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + 32 * j + 8 * c) : zero;
+      qb[j] = r + 8 < G ? *reinterpret_cast<const uint4*>(qrow + (size_t)(r + 8) * HD + 32 * j + 8 * c) : zero;
+    }
+  }
+
+  // scores are kept times log2(e), so that the exponentials are single exp2 steps
+  const float scale2 = scale * 1.4426950408889634f;
+  const bool upper = G > 8;   // rows 8..15 of the tiles hold heads at all
+  float mx[2] = {ATD_NEG, ATD_NEG}, l[2] = {0.f, 0.f};
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; n++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc[n][e] = 0.f;
+
   uint4 kf[4][KB], vf[NT];      // the block being multiplied
   int q_stage = 0;
   for (int blk = blk_lo + warp; blk < blk_hi; blk += ATD_WARPS, q_stage++) {
@@ -319,12 +420,12 @@ LEB_API int leb_attention_decode_supported(int nh, int nkv, int hd, int page_siz
 // The first stage of a decode step's attention: every sequence brings one row.  With
 // n_splits > 1 the partial results go to `part` (same layout as the general kernel's) and the
 // caller merges them.
-LEB_API int leb_attention_decode(void* out, float* part, const void* q, const void* k_pool,
-                                 const void* v_pool, const int* block_table, int bt_width,
-                                 const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
-                                 const void* gate, int gate_stride, int B, int nh, int nkv, int hd,
-                                 int page_size, int window, float scale, int n_splits,
-                                 cudaStream_t st) {
+static int attention_decode_launch(void* out, float* part, const void* q, const void* k_pool,
+                                   const void* v_pool, const int* block_table, int bt_width,
+                                   const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
+                                   const void* gate, int gate_stride, int B, int nh, int nkv, int hd,
+                                   int page_size, int window, float scale, int n_splits, AtdPrep prep,
+                                   cudaStream_t st) {
   if (B <= 0) return 0;
   LEB_REQUIRE(leb_attention_decode_supported(nh, nkv, hd, page_size),
               "leb_attention_decode: sizes not taken (heads %d, kv heads %d, head_dim %d, page %d)", nh, nkv, hd, page_size);
@@ -343,15 +444,9 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
     leb_launch(attention_decode_kernel<HD_, S_>, grid, dim3(32 * ATD_WARPS), smem, st,             \
         (bf16*)out, part, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,  \
         bt_width, seq_slot, seq_pos0, seq_qstart, (const bf16*)gate, gate_stride, nh, nkv, page_size, \
-        window, scale, n_splits);                                                                 \
+        window, scale, n_splits, prep);                                                           \
   }
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-  }
-  const bool few = (long)grid.x * grid.y * grid.z <= 2L * n_sm;   // an SM gets two blocks at most: deeper rings
+  const bool few = (long)grid.x * grid.y * grid.z <= 2L * sm_count();   // an SM gets two blocks at most: deeper rings
   switch (hd) {
     case 32: LEB_ATD(32, 3); break;
     case 64: if (few) LEB_ATD(64, 3) else LEB_ATD(64, 2) break;
@@ -361,6 +456,44 @@ LEB_API int leb_attention_decode(void* out, float* part, const void* q, const vo
 #undef LEB_ATD
   LEB_CHECK_LAUNCH("leb_attention_decode");
   return 0;
+}
+
+LEB_API int leb_attention_decode(void* out, float* part, const void* q, const void* k_pool,
+                                 const void* v_pool, const int* block_table, int bt_width,
+                                 const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
+                                 const void* gate, int gate_stride, int B, int nh, int nkv, int hd,
+                                 int page_size, int window, float scale, int n_splits,
+                                 cudaStream_t st) {
+  return attention_decode_launch(out, part, q, k_pool, v_pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, gate,
+                                 gate_stride, B, nh, nkv, hd, page_size, window, scale, n_splits, AtdPrep{}, st);
+}
+
+// Returns 1 when the kernel can norm, rotate and store the step's q, k and v itself: head size 64 or
+// 128 and a split-half rotation over the whole head.
+LEB_API int leb_attention_decode_prep_supported(int nh, int nkv, int hd, int page_size, int rope_dim, int neox) {
+  return leb_attention_decode_supported(nh, nkv, hd, page_size) && (hd == 64 || hd == 128) && rope_dim == hd && neox != 0;
+}
+
+// The same with the step's q, k and v as the projection left them (rows of q_stride / kv_stride
+// values; k_raw and v_raw null for a layer that stores no keys): per-head norm (weights may be
+// null), rotation by position * inv_freq and the write of the new key and value into the pools
+// happen inside the kernel.
+LEB_API int leb_attention_decode_prep(void* out, float* part, const void* q_raw, int q_stride, const void* k_raw,
+                                      const void* v_raw, int kv_stride, void* k_pool, void* v_pool,
+                                      const int* block_table, int bt_width, const int* seq_slot,
+                                      const int* seq_pos0, const int* seq_qstart, const float* q_norm_w,
+                                      const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
+                                      int neox, const void* gate, int gate_stride, int B, int nh, int nkv,
+                                      int hd, int page_size, int window, float scale, int n_splits,
+                                      cudaStream_t st) {
+  LEB_REQUIRE(leb_attention_decode_prep_supported(nh, nkv, hd, page_size, rope_dim, neox),
+              "leb_attention_decode_prep: sizes not taken (head_dim %d, rope_dim %d, split-half %d)", hd, rope_dim, neox);
+  LEB_REQUIRE(q_raw && inv_freq, "leb_attention_decode_prep: q and the frequencies are required");
+  LEB_REQUIRE((k_raw == nullptr) == (v_raw == nullptr), "leb_attention_decode_prep: keys and values come together");
+  AtdPrep prep{(const bf16*)q_raw, (const bf16*)k_raw, (const bf16*)v_raw, q_stride, kv_stride, (bf16*)k_pool,
+               (bf16*)v_pool, q_norm_w, k_norm_w, inv_freq, eps};
+  return attention_decode_launch(out, part, nullptr, k_pool, v_pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart,
+                                 gate, gate_stride, B, nh, nkv, hd, page_size, window, scale, n_splits, prep, st);
 }
 
 // ---- the same step for callers that cannot allocate (see leb_no_alloc.h) ---------------------------

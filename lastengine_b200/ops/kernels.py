@@ -120,6 +120,8 @@ def _declare(L) -> None:
         "leb_attention_decode_supported": [I, I, I, I],
         "leb_attention_decode": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_merge": [P, P, I, P, I, I, I, I, I, P],
+        "leb_attention_decode_prep_supported": [I, I, I, I, I, I],
+        "leb_attention_decode_prep": [P, P, P, I, P, P, I, P, P, P, I, P, P, P, P, P, F, P, I, I, P, I, I, I, I, I, I, I, F, I, P],
         "leb_attention_prefill_supported": [I, I, I, I],
         "leb_attention_prefill_tc_supported": [I, I, I, I],
         "leb_attention_prefill_tc": [P, P, I, I, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
@@ -127,6 +129,7 @@ def _declare(L) -> None:
         "leb_gemm_bf16_skinny_slices": [I, I],
         "leb_gemm_bf16_skinny_supported": [P, P, I, I, I],
         "leb_gemm_bf16_skinny": [P, I, P, P, I, I, I, I, I, I, P, I, P, I, I, F, P, P, P, P, P],
+        "leb_gemm_bf16_skinny_conv": [P, P, P, I, I, I, I, I, P, P, P, P, P, I, P, I, P, I, I, F, P, P],
         "leb_gemm_bf16_tc_supported": [P, P, I, I],
         "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
         "leb_selftest_bounded_wait": [P, I, I, P],
@@ -269,15 +272,35 @@ CONV_FUSED_MAX_LC = 5    # conv lengths the fused decode kernel takes
 def shortconv_decode_fused(y: torch.Tensor, h: torch.Tensor, w_in: torch.Tensor, w: torch.Tensor,
                            bias: torch.Tensor | None, state: torch.Tensor, batch, Lc: int,
                            scale: "SplitNorm | None" = None) -> bool:
-    """The conv mixer's in_proj and convolution of a decode step in one launch: y = conv(h . w_in^T),
-    state updated.  False (nothing done) when the step is not one of up to SMALL_M sequences with
-    one bfloat16 row each, or the sizes are not the kernel's."""
+    """The conv mixer's in_proj and convolution of a decode step without a kernel of the
+    convolution's own: y = conv(h . w_in^T), state updated.  Up to SMALL_M sequences it is the epilogue
+    of the weight stream (one launch); up to SKINNY_M sequences the second kernel of the sliced
+    tcgen05 product.  False (nothing done) when the step is not one of so many sequences with one
+    bfloat16 row each, or the sizes are not the kernels'."""
     M, D = y.shape
     K = h.shape[1]
-    if not (h.dtype == torch.bfloat16 and y.dtype == torch.bfloat16 and 0 < M <= SMALL_M
+    if not (h.dtype == torch.bfloat16 and y.dtype == torch.bfloat16 and 0 < M <= SKINNY_M
             and batch.max_qlen == 1 and M == batch.n_seqs and 2 <= Lc <= CONV_FUSED_MAX_LC and K % 8 == 0
             and h.stride(0) % 8 == 0 and h.stride(1) == 1 and y.stride(1) == 1):
         return False
+    if M > SMALL_M:
+        L = lib()
+        slices = L.leb_gemm_bf16_skinny_slices(3 * D, K)
+        if slices < 2 or 3 * D >= SKINNY_MAX_N or not _tma_ok(h, w_in, K) or not w_in.is_contiguous():
+            return False
+        _cuda(w_in, "shortconv.w_in", torch.bfloat16)
+        _cuda(w, "shortconv.w", torch.float32)
+        _cuda(state, "shortconv.state", torch.float32)
+        assert w_in.shape == (3 * D, K) and w.numel() == D * Lc and state.shape[1:] == (D, Lc - 1)
+        if bias is not None:
+            _cuda(bias, "shortconv.bias", torch.float32)
+        ssq, parts, d_in, eps = _scale_args(scale, M, K)
+        part = _skinny_workspace(h.device, slices * M * 3 * D)
+        _check(L.leb_gemm_bf16_skinny_conv(_ptr(y), _ptr(h), _ptr(w_in), M, D, K, h.stride(0), y.stride(0), _ptr(w),
+                                           _ptr(bias), _ptr(state), _ptr(batch.row_seq), _ptr(batch.seq_slot), Lc,
+                                           _ptr(part), slices, ssq, parts, d_in, eps, _ptr(_status_word(h.device)),
+                                           _stream()))
+        return True
     _cuda(h, "shortconv.h", contiguous=False)
     _cuda(w_in, "shortconv.w_in", torch.bfloat16)
     _cuda(w, "shortconv.w", torch.float32)
@@ -341,15 +364,17 @@ def sm_count() -> int:
     return n
 
 
-def attention_splits(batch, nkv: int, G: int, sm_count: int | None = None) -> int:
+def attention_splits(batch, nkv: int, G: int, sm_count: int | None = None, hd: int = 64) -> int:
     """How many blocks share one sequence's key range in a decode step (1 for prompts).
 
-    Measured on B200 (head size 64, 8 kv heads): about 1024 positions per block is best with many
-    sequences, with few sequences more splits are worth it until some 128 blocks run, and a
-    split count that needs one more wave of blocks than the GPU holds at once (two per SM) costs
-    more than it saves.  The count with the least (waves x positions per block, in units of 32)
-    plus half a unit per split (and per wave of
-    rows) for the merge is taken; a block gets at least 128 positions.
+    Measured on B200 (head size 64, 8 kv heads, times with the merge of the splits): a block has a
+    fixed cost of some microseconds, so a split must leave a block 256 positions or more (128 when
+    there are so few blocks that the step waits on each one's latency); the blocks
+    of a launch should all run at once (three per SM at head size 64: with 8 sequences of 4,096
+    positions 6 splits, 384 blocks, take 14.7 us a layer and 7 splits, 448 blocks, 18.8 us); and
+    when the sequences alone fill the GPU twice over, splitting pays only for long ranges (64
+    sequences of 640 positions: 20.3 us unsplit, 27.4 us in 4 splits; of 4,096 positions: 110 us
+    unsplit, 89 us in 4 splits).
     """
     if batch.max_qlen != 1:
         return 1
@@ -357,26 +382,46 @@ def attention_splits(batch, nkv: int, G: int, sm_count: int | None = None) -> in
         sm_count = globals()["sm_count"]()
     kv = max(int(batch.max_kvlen), 1)
     per = max(batch.n_seqs * nkv * ((G + 15) // 16), 1)
-    best, best_cost = 1, None
-    for n in range(1, 33):
-        each = -(-kv // n)
-        if n > 1 and each < 128:
-            break
-        cost = -(-per * n // (2 * sm_count)) * -(-each // 32) + 0.5 * n * max(1.0, per / (2 * sm_count))
-        if best_cost is None or cost < best_cost:
-            best, best_cost = n, cost
-    return best
+    stage_bytes = 2 * 32 * hd * 2 * (3 if hd <= 32 else 2) * 4          # a block's rings: 4 warps, keys and values
+    slots = sm_count * max(1, min(3, (227 * 1024) // stage_bytes))      # blocks that run at once
+    if per >= 2 * sm_count:
+        return 1 if kv < 2048 else min(4, kv // 1024)
+    least = 128 if per * 8 <= sm_count else 256       # one or two sequences: latency counts, shorter blocks pay
+    return max(1, min(slots // per, kv // least, 32))
 
 
 TC_ATTENTION_MIN_ROWS = 8   # longest row count of a sequence from which prompts go to the tcgen05 attention
 
 
-def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+class RawQKV:
+    """A decode step's q, k and v as the projection left them, for the decode attention kernel that
+    norms, rotates and stores them itself (`decode_attention_takes_raw` says when it can)."""
+
+    def __init__(self, q_in, k_in, v_in, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox):
+        self.q_in, self.k_in, self.v_in = q_in, k_in, v_in
+        self.q_norm_w, self.k_norm_w, self.eps = q_norm_w, k_norm_w, float(eps)
+        self.inv_freq, self.rope_dim, self.neox = inv_freq, int(rope_dim), bool(neox)
+
+
+def decode_attention_takes_raw(dtype: torch.dtype, batch, M: int, nh: int, nkv: int, hd: int, page_size: int,
+                               inv_freq, rope_dim: int, neox: bool) -> bool:
+    """Whether `attention(..., raw=...)` will do the per-head norm, the rotation and the cache write
+    of this step itself: a bfloat16 decode step (one row per sequence) whose sizes the tensor-core
+    decode kernel takes, with a split-half rotation over the whole head."""
+    return bool(dtype == torch.bfloat16 and batch.max_qlen == 1 and M == batch.n_seqs and inv_freq is not None
+                and lib().leb_attention_decode_prep_supported(nh, nkv, hd, page_size, int(rope_dim), 1 if neox else 0))
+
+
+def attention(out: torch.Tensor, q: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor,
               block_table: torch.Tensor, batch, nh: int, nkv: int, hd: int, page_size: int,
               window: int, scale: float, gate: torch.Tensor | None = None,
-              n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
-    """Causal attention of the step's rows over the paged cache (which already holds their keys)."""
+              n_splits: int = 1, scratch: torch.Tensor | None = None, raw: RawQKV | None = None) -> None:
+    """Causal attention of the step's rows over the paged cache (which already holds their keys;
+    with `raw`, the kernel puts the step's keys and values there itself and `q` is not used)."""
     _cuda(out, "attention.out")
+    if raw is not None:
+        return _attention_decode_raw(out, raw, k_pool, v_pool, block_table, batch, nh, nkv, hd, page_size, window,
+                                     scale, gate, n_splits, scratch)
     _cuda(q, "attention.q", out.dtype)
     _cuda(k_pool, "attention.k_pool", out.dtype)
     _cuda(v_pool, "attention.v_pool", out.dtype)
@@ -430,6 +475,48 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
         _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(gate), gate_stride, M, batch.n_seqs, nh, nkv,
         hd, page_size, window, float(scale), batch.max_qlen, n_splits, _stream()))
+
+
+def _attention_decode_raw(out, raw: RawQKV, k_pool, v_pool, block_table, batch, nh, nkv, hd, page_size, window,
+                          scale, gate, n_splits, scratch) -> None:
+    M = out.shape[0]
+    if not decode_attention_takes_raw(out.dtype, batch, M, nh, nkv, hd, page_size, raw.inv_freq, raw.rope_dim, raw.neox):
+        raise KernelError("attention: this step's q, k and v must be normed, rotated and stored before the call")
+    _cuda(k_pool, "attention.k_pool", out.dtype)
+    _cuda(v_pool, "attention.v_pool", out.dtype)
+    _cuda(block_table, "attention.block_table", torch.int32)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, hd, page_size)
+    _cuda(raw.q_in, "attention.q_in", out.dtype, contiguous=False)
+    assert raw.q_in.shape == (M, nh * hd) and raw.q_in.stride(-1) == 1 and out.shape == (M, nh * hd)
+    kv_stride = 0
+    if raw.k_in is not None:
+        _cuda(raw.k_in, "attention.k_in", out.dtype, contiguous=False)
+        _cuda(raw.v_in, "attention.v_in", out.dtype, contiguous=False)
+        assert raw.k_in.shape == (M, nkv * hd) and raw.v_in.shape == (M, nkv * hd)
+        assert raw.k_in.stride(0) == raw.v_in.stride(0) and raw.k_in.stride(-1) == 1 and raw.v_in.stride(-1) == 1
+        kv_stride = raw.k_in.stride(0)
+    for name, t in (("q_norm_w", raw.q_norm_w), ("k_norm_w", raw.k_norm_w), ("inv_freq", raw.inv_freq)):
+        if t is not None:
+            _cuda(t, f"attention.{name}", torch.float32)
+    assert raw.inv_freq.numel() == hd // 2
+    gate_stride = 0
+    if gate is not None:
+        _cuda(gate, "attention.gate", out.dtype, contiguous=False)
+        assert gate.shape == (M, nh) and gate.stride(-1) == 1
+        gate_stride = gate.stride(0)
+    if n_splits > 1:
+        need = M * nh * n_splits * (hd + 2)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention: {n_splits} splits need {need} floats of scratch")
+    L = lib()
+    _check(L.leb_attention_decode_prep(
+        _ptr(out), _ptr(scratch), _ptr(raw.q_in), raw.q_in.stride(0), _ptr(raw.k_in), _ptr(raw.v_in), kv_stride,
+        _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
+        _ptr(batch.seq_qstart), _ptr(raw.q_norm_w), _ptr(raw.k_norm_w), raw.eps, _ptr(raw.inv_freq), raw.rope_dim,
+        1 if raw.neox else 0, _ptr(gate), gate_stride, batch.n_seqs, nh, nkv, hd, page_size, window, float(scale),
+        n_splits, _stream()))
+    if n_splits > 1:
+        _check(L.leb_attention_merge(_ptr(out), _ptr(scratch), BF16, _ptr(gate), gate_stride, M, nh, hd, n_splits, _stream()))
 
 
 # ----------------------------------------------------------------------------------------------
@@ -801,8 +888,6 @@ def linear_skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue:
         return False
     slices = L.leb_gemm_bf16_skinny_slices(N, K)
     ssq, parts, d_in, eps, ev, eg, es = norm_args or (None, 0, 0, 0.0, None, None, None)
-    if epilogue == SWIGLU or ssq is not None or ev is not None:
-        slices = max(slices, 2)
     part = _skinny_workspace(x.device, slices * M * N) if slices > 1 else None
     _check(L.leb_gemm_bf16_skinny(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                                   out.stride(0), epilogue, _ptr(part), slices, ssq, parts, d_in, eps, ev, eg, es,

@@ -106,7 +106,11 @@ class AttentionMixer(Mixer):
         q = ws.get("attn.q", (M, nh * hd), env.dtype)
         kp, vp = (cache.k, cache.v) if writes else (None, None)
         rotary = self.position.fused_rotary()
-        if rotary is not None:
+        raw = None
+        if rotary is not None and kernels.decode_attention_takes_raw(env.dtype, batch, M, nh, nkv, hd, cache.page_size, *rotary):
+            # a decode step: the attention kernel norms and rotates q and k and stores k and v itself
+            raw = kernels.RawQKV(q_in, k_in, v_in, self.q_norm_w, self.k_norm_w if writes else None, self.eps, *rotary)
+        elif rotary is not None:
             # per-head norm, rotation and the cache write in one launch
             kernels.qk_rope_store(q, q_in, k_in, v_in, kp, vp, cache.block_table, batch, self.q_norm_w,
                                   self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, hd, cache.page_size)
@@ -127,11 +131,11 @@ class AttentionMixer(Mixer):
             kernels.qk_rope_store(q, qn, kn, vn, kp, vp, cache.block_table, batch, None, None, self.eps,
                                   None, 0, True, nh, nkv, hd, cache.page_size)
         o = ws.get("attn.o", (M, nh * hd), env.dtype)
-        n_splits = kernels.attention_splits(batch, nkv, nh // nkv)
+        n_splits = kernels.attention_splits(batch, nkv, nh // nkv, hd=hd)
         scratch = None
         if n_splits > 1:
             scratch = ws.get("attn.part", (M * nh * n_splits * (hd + 2),), torch.float32)
-        kernels.attention(o, q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd, cache.page_size,
-                          self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch)
+        kernels.attention(o, None if raw is not None else q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd,
+                          cache.page_size, self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch, raw=raw)
         kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE,
                        emit=emit if accumulate else None)

@@ -313,9 +313,11 @@ def test_shortconv_many_rows(Lc, D):
         assert err(state[slots[i]].cpu().T, padded[-(Lc - 1):]) < 1e-6, i
 
 
-@pytest.mark.parametrize("B,D,K_,Lc", [(8, 2048, 2048, 3), (1, 72, 40, 2), (13, 136, 200, 4), (16, 48, 64, 5), (5, 100, 72, 3)])
+@pytest.mark.parametrize("B,D,K_,Lc", [(8, 2048, 2048, 3), (1, 72, 40, 2), (13, 136, 200, 4), (16, 48, 64, 5), (5, 100, 72, 3),
+                                       (40, 2048, 2048, 3), (100, 136, 1024, 4), (18, 48, 512, 5)])
 def test_shortconv_decode_fused(B, D, K_, Lc):
-    """Projection and convolution of a decode step in one launch, three steps in a row so that the
+    """Projection and convolution of a decode step without a convolution kernel (up to 16 sequences:
+    one launch; more: the sliced product, whose second kernel convolves), three steps in a row so that the
     state it writes is the state it reads next; one sequence is padding, the slots are not in order
     and other slots hold stale values.  Compared with the plain formulas (projection rounded to
     bfloat16 as the two-kernel path stores it) and with the two-kernel path itself."""
@@ -323,6 +325,7 @@ def test_shortconv_decode_fused(B, D, K_, Lc):
     w_in = gen(3 * D, K_, seed=63, scale=0.05, dtype=torch.bfloat16)
     w = gen(D, Lc, seed=64)
     slots = [(5 * i + 3) % (B + 3) for i in range(B)]
+    assert len(set(slots)) == B
     if B > 2:
         slots[1] = -1
     state = torch.full((B + 3, D, Lc - 1), 7.0, device=DEV)
@@ -461,6 +464,72 @@ def fill_cache(k, v, pages, nkv, hd, page, dtype):
         kp[pages[t // page], :, t % page] = k[t].to(dtype)
         vp[pages[t // page], :, :, t % page] = v[t].to(dtype)
     return kp.to(DEV), vp.to(DEV)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 8, 64), (6, 2, 128), (5, 5, 64), (16, 1, 64)])
+@pytest.mark.parametrize("window,gated,with_norm", [(0, False, True), (40, True, True), (0, False, False)])
+def test_decode_attention_that_norms_rotates_and_stores_the_step_itself(nh, nkv, hd, window, gated, with_norm):
+    """A decode step handed to the attention kernel as the projection left it (raw q, k and v) against
+    the same step with the rotary kernel first: the same output bits and the same cache, at every
+    split count, for sequences whose new position starts a page, ends one, or is the first of all;
+    a padding sequence among them; and against double-precision arithmetic."""
+    page, dtype = 64, torch.bfloat16
+    lens = [130, 1, 64, 65, 257, 7]                 # lengths after the step: the new token sits at len - 1
+    slots = [0, 1, -1, 2, 3, 4]
+    B = len(lens)
+    width = max(-(-n // page) for n in lens)
+    n_pages = B * width + 1
+    order = np.random.default_rng(6).permutation(n_pages)[:B * width].astype(np.int32).reshape(B, width)
+    kp0 = gen(n_pages, nkv, page, hd, seed=50, dtype=dtype).to(DEV)
+    vp0 = gen(n_pages, nkv, hd, page, seed=51, dtype=dtype).to(DEV)
+    qkv = gen(B, (nh + 2 * nkv) * hd + nh, seed=52, dtype=dtype).to(DEV)        # q | k | v | gate as one projection
+    q_in, k_in = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd]
+    v_in, gate = qkv[:, (nh + nkv) * hd:(nh + 2 * nkv) * hd], (qkv[:, (nh + 2 * nkv) * hd:] if gated else None)
+    qn = (1 + 0.1 * gen(hd, seed=53)).to(DEV) if with_norm else None
+    kn = (1 + 0.1 * gen(hd, seed=54)).to(DEV) if with_norm else None
+    theta, eps, scale = 5e4, 1e-5, 1 / math.sqrt(hd)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    batch = builder().build(slots, [[0]] * B, [n - 1 for n in lens], [], {0: order})
+    assert K().decode_attention_takes_raw(dtype, batch, B, nh, nkv, hd, page, inv, hd, True)
+    for splits in (1, 2, 5):
+        scratch = torch.empty(B * nh * splits * (hd + 2), device=DEV)
+        # the two-kernel way
+        kp_a, vp_a = kp0.clone(), vp0.clone()
+        q_rot = torch.empty(B, nh * hd, device=DEV, dtype=dtype)
+        K().qk_rope_store(q_rot, q_in, k_in, v_in, kp_a, vp_a, batch.tables[0], batch, qn, kn, eps, inv, hd, True, nh, nkv, hd, page)
+        want = torch.empty(B, nh * hd, device=DEV, dtype=dtype)
+        K().attention(want, q_rot, kp_a, vp_a, batch.tables[0], batch, nh, nkv, hd, page, window, scale, gate=gate,
+                      n_splits=splits, scratch=scratch)
+        # the kernel that does it all
+        kp_b, vp_b = kp0.clone(), vp0.clone()
+        got = torch.full_like(want, float("nan"))
+        K().attention(got, None, kp_b, vp_b, batch.tables[0], batch, nh, nkv, hd, page, window, scale, gate=gate,
+                      n_splits=splits, scratch=scratch, raw=K().RawQKV(q_in, k_in, v_in, qn, kn, eps, inv, hd, True))
+        torch.cuda.synchronize()
+        assert torch.equal(kp_a, kp_b) and torch.equal(vp_a, vp_b), f"{splits} splits: the caches differ"
+        assert not torch.equal(kp_a, kp0)
+        assert torch.equal(got, want), f"{splits} splits: {err(got, want):.3e}"
+    # against double precision, from the cache the kernel left
+    for b, n in enumerate(lens):
+        if slots[b] < 0:
+            assert float(got[b].float().abs().max()) == 0.0
+            continue
+        k = torch.stack([kp_b[int(order[b, t // page]), :, t % page].double().cpu() for t in range(n)])
+        v = torch.stack([vp_b[int(order[b, t // page]), :, :, t % page].double().cpu() for t in range(n)])
+        row = qkv[b].double().cpu()
+        q = row[:nh * hd].view(1, nh, hd)
+        if with_norm:
+            q = P.rms_norm(q, qn.double().cpu(), eps)
+        q = P.round_bf16(P.rope(q, torch.tensor([n - 1]), hd, theta))
+        o = plain_attention(q, k, v, torch.tensor([n - 1]), window, scale)[0]
+        if gated:
+            o = o * torch.sigmoid(row[(nh + 2 * nkv) * hd:])[:, None]
+        assert err(got[b].view(nh, hd), o) < 8e-3, b
+        # the new key is the normed and rotated one
+        kn_new = row[nh * hd:(nh + nkv) * hd].view(1, nkv, hd)
+        if with_norm:
+            kn_new = P.rms_norm(kn_new, kn.double().cpu(), eps)
+        assert err(k[n - 1], P.rope(kn_new, torch.tensor([n - 1]), hd, theta)[0]) < 6e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
