@@ -869,3 +869,4 @@ def test_linear_skinny_swiglu(M, F, D):
     assert K().linear_skinny(out, x.to(DEV), fuse_gate_up(w1, w3, True).to(DEV), K().SWIGLU)
     K().check_device_status()
     assert err(out, want) < 6e-3
+
