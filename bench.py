@@ -234,7 +234,8 @@ KERNEL_CLASSES = {
     "leb_gemm_bf16_stream": "weight-streaming products", "leb_gemm_bf16_stream_conv": "weight-streaming products",
     "leb_gemm_bf16_stream_grouped": "weight-streaming products", "leb_gemm_bf16_skinny": "weight-streaming products",
     "leb_gemm_bf16_small": "weight-streaming products",
-    "leb_attention_decode": "decode attention", "leb_attention_merge": "decode attention",
+    "leb_attention_decode": "decode attention", "leb_attention_decode_prep": "decode attention",
+    "leb_attention_merge": "decode attention",
     "leb_gemm_bf16_tc": "tcgen05 products", "leb_gemm_bf16_tc2": "tcgen05 products", "leb_gemm_bf16_tc_grouped": "tcgen05 products",
     "leb_attention_prefill_tc": "tcgen05 prompt attention", "leb_attention_prefill": "prompt attention",
 }
