@@ -229,6 +229,20 @@ struct FinishConv {
 };
 #define SK_CONV_MAX_LC 5
 
+// One element's partial sums added in slice order.  Eight loads are issued before the first is
+// used: a thread that fetched one slice at a time spent a round trip to L2 on each.
+__device__ __forceinline__ float sum_slices(const float* __restrict__ p, size_t slab, int n_slices) {
+  float a = 0.f;
+  for (int s0 = 0; s0 < n_slices; s0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) v[u] = s0 + u < n_slices ? __ldcs(p + (size_t)(s0 + u) * slab) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) a += v[u];
+  }
+  return a;
+}
+
 // Adds the slices in order and applies the epilogue.  part: [slices][M][N] float.
 template <typename TC>
 __global__ void __launch_bounds__(256)
@@ -257,13 +271,9 @@ skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, 
     // had been stored, taps oldest first, the state shifted by one (shortconv.cu, one-token form).
     const int D = N / 3;
     if (j >= D) return;
-    float pb = 0.f, pc = 0.f, px = 0.f;
-    for (int s = 0; s < n_slices; s++) {
-      const float* p = part + s * slab + (size_t)m * N + j;
-      pb += p[0];
-      pc += p[D];
-      px += p[2 * D];
-    }
+    const float* p0 = part + (size_t)m * N + j;
+    const float pb = sum_slices(p0, slab, n_slices), pc = sum_slices(p0 + D, slab, n_slices),
+                px = sum_slices(p0 + 2 * D, slab, n_slices);
     TC* yo = C + (size_t)m * ldc + j;
     const int slot = cv.seq_slot[cv.row_seq[m]];
     if (slot < 0) {   // padding row
@@ -291,21 +301,15 @@ skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, 
     // column n = 32*(j/16) + (j%16) is the gate of output j, n + 16 its up value
     if (j >= N / 2) return;
     const int n = 32 * (j >> 4) + (j & 15);
-    float g = 0.f, u = 0.f;
-    for (int s = 0; s < n_slices; s++) {
-      g += part[s * slab + (size_t)m * N + n];
-      u += part[s * slab + (size_t)m * N + n + 16];
-    }
-    g *= r;
-    u *= r;
+    const float g = sum_slices(part + (size_t)m * N + n, slab, n_slices) * r;
+    const float u = sum_slices(part + (size_t)m * N + n + 16, slab, n_slices) * r;
     C[(size_t)m * ldc + j] = from_f32<TC>(g / (1.0f + expf(-g)) * u);
     return;
   }
   const bool in = j < N;
   float a = 0.f;
   if (in) {
-    for (int s = 0; s < n_slices; s++) a += part[s * slab + (size_t)m * N + j];
-    a *= r;
+    a = sum_slices(part + (size_t)m * N + j, slab, n_slices) * r;
     TC* o = C + (size_t)m * ldc + j;
     if (epilogue == 1) a += to_f32(*o);
     *o = from_f32<TC>(a);
