@@ -195,6 +195,7 @@ template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
                                        const T* __restrict__ gate, int gate_stride, int nh, int hd,
                                        int n_splits) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const size_t m = blockIdx.x;
   const int h = blockIdx.y;

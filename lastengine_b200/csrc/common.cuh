@@ -47,6 +47,14 @@ static inline cudaError_t leb_launch(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.numAttrs = g_leb_pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+// silu(g) * u.  The bfloat16 products' epilogues take 2^x and the reciprocal from the special
+// function unit (relative error about 1e-6, far below the rounding of the bfloat16 they store):
+// with exact expf and division an epilogue of a few warps is bound by its instructions.
+template <typename T>
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  if (sizeof(T) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  return g / (1.0f + expf(-g)) * u;
+}
 // Device side.  pdl_trigger(): the next kernel on the stream may be scheduled (once every block
 // of this one has said so); it then runs its own start-up and waits in its pdl_wait() until this
 // kernel has completed.  Said first thing, even before this kernel's own wait: a product two

@@ -26,6 +26,7 @@ LEB_API long long leb_launch_count() { return g_leb_launches; }
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
                              const int* __restrict__ tokens, int D, int V) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int m = blockIdx.x;
   int tok = tokens[m];
@@ -59,6 +60,7 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
                                const float* __restrict__ w, const int* __restrict__ rows, int D,
                                float eps) {
   __shared__ float red[33];
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int m = blockIdx.x;
   const float* xi = x + (size_t)(rows ? rows[m] : m) * D;
@@ -86,6 +88,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_bf16_vec_kernel(bf16* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                         const int* __restrict__ rows, int D, float eps) {
   __shared__ float red[33];
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m = blockIdx.x;
   const float4* xi = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[m] : m) * D);
@@ -155,7 +158,7 @@ __global__ void swiglu_kernel(TO* __restrict__ a, const TI* __restrict__ gu, int
   int j = (int)(i - m * F);
   float g = to_f32(gu[m * 2 * F + j]);
   float u = to_f32(gu[m * 2 * F + F + j]);
-  a[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+  a[i] = from_f32<TO>(silu_mul<TO>(g, u));
 }
 
 LEB_API int leb_swiglu(void* a, int out_dtype, const void* gu, int in_dtype, int M, int F,
@@ -180,6 +183,7 @@ LEB_API int leb_swiglu(void* a, int out_dtype, const void* gu, int in_dtype, int
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in,
                                    const int* __restrict__ rows, int div, int D) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int p = blockIdx.x;
   int src = rows[p] / div;

@@ -53,6 +53,7 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
         asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
     }
   }
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   if (group_offsets) {
     row_begin = group_offsets[blockIdx.z];
@@ -141,7 +142,7 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
         g += red[w][0][i][col];
         u += red[w][NSUB - 1][i][col];
       }
-      C[(size_t)m * ldc + jbase + i] = from_f32<TC>(g / (1.0f + expf(-g)) * u);
+      C[(size_t)m * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(g, u));
     }
     return;
   }

@@ -256,7 +256,7 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
         }
         gt *= row_scale[col];
         up *= row_scale[col];
-        C[(size_t)col * ldc + jbase + i] = from_f32<TC>(gt / (1.0f + expf(-gt)) * up);
+        C[(size_t)col * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(gt, up));
       }
     } else {
       const int n0 = tile * ROWS;
@@ -434,7 +434,7 @@ gemm_bf16_stream_grouped_kernel(TC* __restrict__ C, const bf16* __restrict__ A, 
           gt += red[w][0][i][col];
           up += red[w][NSUB - 1][i][col];
         }
-        C[(size_t)(ct.row0 + col) * ldc + jbase + i] = from_f32<TC>(gt / (1.0f + expf(-gt)) * up);
+        C[(size_t)(ct.row0 + col) * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(gt, up));
       }
     } else {
       for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {

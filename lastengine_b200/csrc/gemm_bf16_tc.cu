@@ -203,7 +203,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const float g = __uint_as_float(v[i + e]), u = __uint_as_float(v[16 + i + e]);
-              fp[e] = g / (1.0f + expf(-g)) * u;
+              fp[e] = silu_mul<TC>(g, u);
             }
             *reinterpret_cast<float4*>(mine + i) = f;
           }

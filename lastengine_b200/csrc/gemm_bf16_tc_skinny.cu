@@ -174,7 +174,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const float gt = __uint_as_float(v[i]) * rs;
             const float up = __shfl_down_sync(0xffffffffu, gt, 16);
             if (lane < 16 && c0 + i < M && 2 * j < N) {
-              const float a = gt / (1.0f + expf(-gt)) * up;
+              const float a = c_dtype == LEB_F32 ? silu_mul<float>(gt, up) : silu_mul<bf16>(gt, up);
               if (c_dtype == LEB_F32) ((float*)C)[(size_t)(c0 + i) * ldc + j] = a;
               else ((bf16*)C)[(size_t)(c0 + i) * ldc + j] = __float2bfloat16_rn(a);
             }
@@ -248,6 +248,7 @@ template <typename TC>
 __global__ void __launch_bounds__(256)
 skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, int N, int ldc, int epilogue,
                      int n_slices, FinishNorm nm, FinishConv cv) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -303,7 +304,7 @@ skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, 
     const int n = 32 * (j >> 4) + (j & 15);
     const float g = sum_slices(part + (size_t)m * N + n, slab, n_slices) * r;
     const float u = sum_slices(part + (size_t)m * N + n + 16, slab, n_slices) * r;
-    C[(size_t)m * ldc + j] = from_f32<TC>(g / (1.0f + expf(-g)) * u);
+    C[(size_t)m * ldc + j] = from_f32<TC>(silu_mul<TC>(g, u));
     return;
   }
   const bool in = j < N;

@@ -27,6 +27,7 @@ moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const 
   float* hs = sm;
   float* s_ = hs + (size_t)R * D;
   float* c_ = s_ + R * E;
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m0 = blockIdx.x * R;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(1024)
 moe_align_kernel(int* __restrict__ offsets, int* __restrict__ sorted_pair, int* __restrict__ pair_row,
                  const int* __restrict__ topk_ids, int P, int E) {
   __shared__ int cnt[32][MOE_MAX_E];
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = ((P + 31) / 32 + 31) / 32 * 32;   // pairs per warp, a multiple of 32
@@ -226,6 +228,7 @@ template <int VEC>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const int* __restrict__ pair_row,
                    const float* __restrict__ topk_w, int D, int k, int accumulate) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const size_t m = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;

@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     const float* __restrict__ inv_freq, int rope_dim, int neox, int M, int nh, int nkv, int hd,
     int page_size) {
   extern __shared__ float sm[];
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if ((int)blockIdx.x >= M) {
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_lanes_kernel(
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp) {
   constexpr int HD = EPL * 32, NP = EPL / 2, U = 4;
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   if ((int)blockIdx.x >= M) {
     if (blockIdx.y == 0)

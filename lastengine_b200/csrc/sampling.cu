@@ -57,6 +57,7 @@ LEB_API int leb_penalties(float* logits, const int* hist, const int* hist_len, i
 __global__ void penalties_slots_kernel(float* __restrict__ logits, const int* __restrict__ hist,
                                        const int* __restrict__ hist_len, const int* __restrict__ seq_slot,
                                        int window, int V, int n, float repeat_penalty, float presence_penalty) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n) return;
@@ -78,6 +79,7 @@ __global__ void penalties_slots_kernel(float* __restrict__ logits, const int* __
 __global__ void history_append_kernel(int* __restrict__ hist, int* __restrict__ hist_len,
                                       const int* __restrict__ seq_slot, const int* __restrict__ chosen,
                                       int window, int n) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n) return;
@@ -141,6 +143,7 @@ static __device__ unsigned long long g_argmax_best[ARGMAX_ROWS];
 
 __global__ void argmax_part_kernel(const float* __restrict__ logits, int V, int per_block) {
   __shared__ unsigned long long best[8];
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const float* l = logits + (size_t)blockIdx.x * V;
   const int lo = blockIdx.y * per_block, hi = min(V, lo + per_block);
@@ -163,6 +166,7 @@ __global__ void argmax_part_kernel(const float* __restrict__ logits, int V, int 
 }
 
 __global__ void argmax_final_kernel(int* __restrict__ out, int n) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -223,6 +227,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const flo
   __shared__ float prob[SMP_MAX_K];
   __shared__ int n_cand, n_list;
   __shared__ unsigned long long bound_s;
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const float* l = logits + (size_t)blockIdx.x * V;
   const int tid = threadIdx.x;
@@ -401,6 +406,7 @@ LEB_API int leb_sample(int* out, const float* logits, const float* u01, int n, i
 __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_pos,
                                int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
                                const int* __restrict__ chosen, int B) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B || seq_slot[b] < 0) return;
@@ -414,6 +420,7 @@ __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ row_p
 // (feed[b] < 0: the token the host staged stays).
 __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ chosen,
                                    const int* __restrict__ feed, int B) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;

@@ -22,6 +22,7 @@ __global__ void shortconv_rows_kernel(T* __restrict__ y, const T* __restrict__ b
                                       const int* __restrict__ row_seq,
                                       const int* __restrict__ seq_slot,
                                       const int* __restrict__ seq_qstart, int D, int Lc) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int m = blockIdx.x;
   int ch = blockIdx.y * blockDim.x + threadIdx.x;
@@ -58,6 +59,7 @@ __global__ void shortconv_rows_bf16x8_kernel(bf16* __restrict__ y, const bf16* _
                                              const float* __restrict__ state, const int* __restrict__ row_seq,
                                              const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                                              int D, int Lc) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m = blockIdx.x;
   const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -130,6 +132,7 @@ __global__ void __launch_bounds__(128) shortconv_rows_bf16x8_chunk_kernel(
     bf16* __restrict__ y, const bf16* __restrict__ bcx, const float* __restrict__ w,
     const float* __restrict__ bias, const float* __restrict__ state, const int* __restrict__ row_seq,
     const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart, int M, int D) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m0 = blockIdx.x * CONV_CHUNK;
   const int ch0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -206,6 +209,7 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
                                        const int* __restrict__ seq_slot,
                                        const int* __restrict__ seq_qstart,
                                        const int* __restrict__ seq_qlen, int D, int Lc) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int b = blockIdx.x;
   int ch = blockIdx.y * blockDim.x + threadIdx.x;
@@ -237,6 +241,7 @@ __global__ void shortconv_single_kernel(T* __restrict__ y, const T* __restrict__
                                         const float* __restrict__ w, const float* __restrict__ bias,
                                         float* __restrict__ state, const int* __restrict__ seq_slot,
                                         const int* __restrict__ seq_qstart, int D, int Lc) {
+  pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int b = blockIdx.x;
   const int ch = blockIdx.y * blockDim.x + threadIdx.x;
