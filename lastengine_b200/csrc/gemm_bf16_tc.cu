@@ -177,6 +177,19 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     place(tile, m0, m_end, n0, w0, nt);
     const uint32_t buf = t & 1;
     const int row_base = m0 + quad * 32;
+    // adding epilogue with 16-byte rows: a lane's eight old values (rows lane/8 + 4j, four columns
+    // from (lane%8)*4) of a 32-column piece; the first piece's are on their way while the products run
+    float4 nxt[8];
+    auto load_old = [&](int c0) {
+      const int col = n0 + c0 + (lane & 7) * 4;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int row = row_base + (lane >> 3) + 4 * j;
+        nxt[j] = (row < m_end && col + 3 < N) ? __ldcs(reinterpret_cast<const float4*>(C + (size_t)row * ldc + col))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    };
+    if (epilogue == 1 && sizeof(TC) == 4 && (ldc % 4 == 0) && (((uintptr_t)C % 16) == 0)) load_old(0);
     bool ok = mbar_wait(&acc_full[buf], (t >> 1) & 1, abort_flag);
     if (!ok && lane == 0) atomicExch(status, 3);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // the warp leaves together
@@ -216,15 +229,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
         const int col = (epilogue == 2 ? ((n0 + c0) >> 1) : (n0 + c0)) + lc;
         if (epilogue == 1 && sizeof(TC) == 4 && vec && col + 3 < n_out) {
-          // adding into the residual: fetch all eight old pieces first, then add and store, so
-          // the eight loads are in flight together instead of one round trip per row
+          // adding into the residual: the old values of this piece were asked for a piece ago (the
+          // first before the products were complete); now ask for the next piece's, so that they
+          // travel under this piece's stores
           float4 old[8];
 #pragma unroll
-          for (int it = 0; it < 8; it++) {
-            const int row = row_base + lr + 4 * it;
-            old[it] = row < m_end ? __ldcs(reinterpret_cast<const float4*>(C + (size_t)row * ldc + col))
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+          for (int it = 0; it < 8; it++) old[it] = nxt[it];
+          if (c0 + 32 < BN) load_old(c0 + 32);
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const int rr = lr + 4 * it, row = row_base + rr;
