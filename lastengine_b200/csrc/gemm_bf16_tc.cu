@@ -30,10 +30,14 @@
 // rows of it, BN weight rows) are counted in the kernel: a running count of tiles per expert in
 // shared memory, and every role walks the tiles b, b + grid, ... of that list.  A tile's last
 // rows may belong to the next expert: they are computed and not stored.
+// Not GROUPED, n_groups > 1: K is cut into that many slices as well (products of a few hundred rows
+// have fewer 128 x BN tiles than there are SMs); tile t is then slice t % slices of tile t / slices,
+// TC is float, C the workspace [slices][M][N] and the epilogue a plain store: a second kernel
+// (slices_finish) adds the slices up in order and applies the real epilogue.
 template <typename TC, int BN, int STAGES, bool GROUPED>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    TC* __restrict__ C, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status,
+                    TC* __restrict__ C_all, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status,
                     const int* __restrict__ group_offsets, int n_groups) {
   __shared__ int g_cum[GROUPED ? TC_MAX_GROUPS + 1 : 1], g_off[GROUPED ? TC_MAX_GROUPS + 1 : 1];
   extern __shared__ uint8_t smem_raw[];
@@ -54,8 +58,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nk = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-  int num_tiles = m_tiles * n_tiles;         // tile t: rows (t % m_tiles), columns (t / m_tiles):
-                                             // blocks running together share weight tiles in L2
+  const int n_slices = GROUPED ? 1 : max(1, n_groups);
+  const int k_per = (nk + n_slices - 1) / n_slices;     // k-blocks of a slice (the last may have fewer)
+  int num_tiles = m_tiles * n_tiles * n_slices;  // tile t: rows (t % m_tiles), columns (t / m_tiles):
+                                                 // blocks running together share weight tiles in L2
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -95,7 +101,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   // where a tile lies: first row of A and C, the row its rows end at, first column of C, first
   // row of W, and the index of its column tile
-  auto place = [&](int tile, int& m0, int& m_end, int& n0, int& w0, int& nt) {
+  auto place = [&](int tile, int& m0, int& m_end, int& n0, int& w0, int& nt, int& kb_lo, int& kb_n) {
+    kb_lo = 0;
+    kb_n = nk;
+    if (!GROUPED && n_slices > 1) {
+      const int slice = tile % n_slices;
+      tile /= n_slices;
+      kb_lo = slice * k_per;
+      kb_n = max(0, min(nk, kb_lo + k_per) - kb_lo);
+    }
     if (GROUPED) {
       int lo = 0, hi = n_groups;   // the expert with g_cum[lo] <= tile < g_cum[lo + 1]
       while (hi - lo > 1) {
@@ -124,15 +138,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0;   // k-slices loaded so far, over all tiles of this block
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m0, m_end, n0, w0, nt;
-        place(tile, m0, m_end, n0, w0, nt);
-        for (int kb = 0; kb < nk; kb++, it++) {
+        int m0, m_end, n0, w0, nt, kb_lo, kb_n;
+        place(tile, m0, m_end, n0, w0, nt, kb_lo, kb_n);
+        for (int kb = 0; kb < kb_n; kb++, it++) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { atomicExch(status, 1); ok = false; break; }
           mbar_expect_tx(&full[s], loads_a ? A_BYTES : B_BYTES);
           // Tiles that share rows of A start their walk over k at different places, so that
           // blocks running in step do not all ask L2 for the same lines at the same moment.
-          const int kk = (kb + nt * 5) % nk;
+          const int kk = kb_lo + (kb + nt * 5) % kb_n;
           if (loads_a) tma_load_2d(sa + s * A_BYTES, &map_a, &full[s], kk * TC_BK, m0);
           else tma_load_2d(sb + s * B_BYTES, &map_w, &full[s], kk * TC_BK, w0);
         }
@@ -150,7 +164,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) { atomicExch(status, 4); ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_acc + buf * BN;
-        for (int kb = 0; kb < nk; kb++, it++) {
+        const int kb_n = n_slices > 1 ? max(0, min(nk, (tile % n_slices + 1) * k_per) - (tile % n_slices) * k_per) : nk;
+        for (int kb = 0; kb < kb_n; kb++, it++) {
           const int s = it % STAGES;
           if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { atomicExch(status, 2); ok = false; break; }
           tc_fence_after();
@@ -173,8 +188,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     float* stg = stage_out + quad * (32 * 36);
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, t++) {
-    int m0, m_end, n0, w0, nt;
-    place(tile, m0, m_end, n0, w0, nt);
+    int m0, m_end, n0, w0, nt, kb_lo, kb_n;
+    place(tile, m0, m_end, n0, w0, nt, kb_lo, kb_n);
+    TC* const C = C_all + (n_slices > 1 ? (size_t)(tile % n_slices) * M * ldc : 0);   // a slice's part of the workspace
     const uint32_t buf = t & 1;
     const int row_base = m0 + quad * 32;
     // adding epilogue with 16-byte rows: a lane's eight old values (rows lane/8 + 4j, four columns
@@ -310,7 +326,7 @@ static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int 
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
   }
   // grouped: the most tiles the offsets can give (every expert may end with a partly filled tile)
-  const long tiles = (long)ceil_div(N, BN) * (ceil_div(M, TC_BM) + (GROUPED ? n_groups : 0));
+  const long tiles = (long)ceil_div(N, BN) * (ceil_div(M, TC_BM) + (GROUPED ? n_groups : 0)) * (!GROUPED && n_groups > 1 ? n_groups : 1);
   dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));
   leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status, group_offsets,
              n_groups);
@@ -357,6 +373,45 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
     return launch_tc<float, 32, 8>(C, ma, mw, M, N, K, ldc, epilogue, status, st);
   }
   return leb_fail("leb_gemm_bf16_tc: unknown C dtype %d", c_dtype);
+}
+
+// Into how many slices of K a product of M rows is cut (1: not at all): with 256-wide tiles fewer
+// than half as many tiles as SMs, K of 4096 or more and at least 16 k-blocks of 64 per slice (the
+// slices' trip through the workspace and the second kernel cost some 6 us: measured at K = 2048,
+// 4 slices of 8 k-blocks made a 512-row product slower, 14 -> 20 us, where K = 5632 gained, 30 -> 27 us,
+// and at 192 rows 29 -> 19 us).  The caller sizes the workspace (slices * M * N floats) with it.
+LEB_API int leb_gemm_bf16_tc_slices(int M, int N, int K) {
+  const int nk = ceil_div(K, TC_BK), n_sm = sm_count();
+  const long tiles = (long)ceil_div(M, TC_BM) * ceil_div(N, 256);
+  if (N < 256 || nk < 64 || tiles * 2 > n_sm) return 1;
+  int s = (int)(n_sm / tiles);
+  if (s > nk / 16) s = nk / 16;
+  if (s > 8) s = 8;
+  if (s < 2) return 1;
+  const int per = ceil_div(nk, s);
+  return ceil_div(nk, per);
+}
+
+// The product with K cut into n_slices (from leb_gemm_bf16_tc_slices): the slices' partial tiles go to
+// `part` [n_slices][M][N] float, and the second kernel of the sliced decode product adds them up in
+// slice order and applies the epilogue.
+LEB_API int leb_gemm_bf16_tc_sliced(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
+                                    int ldc, int epilogue, float* part, int n_slices, int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc_sliced: operands not aligned for TMA (K %d, lda %d)", K, lda);
+  LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_tc_sliced: unknown epilogue %d", epilogue);
+  LEB_REQUIRE(epilogue != 1 || c_dtype == LEB_F32, "leb_gemm_bf16_tc_sliced: adding needs a float C");
+  LEB_REQUIRE(epilogue != 2 || N % 32 == 0, "leb_gemm_bf16_tc_sliced: the SwiGLU epilogue needs N (%d) to be a multiple of 32", N);
+  LEB_REQUIRE(status != nullptr && part != nullptr, "leb_gemm_bf16_tc_sliced: a status word and the slices' workspace are required");
+  const int nk = ceil_div(K, TC_BK);
+  LEB_REQUIRE(n_slices >= 2 && n_slices <= nk && ceil_div(nk, ceil_div(nk, n_slices)) == n_slices,
+              "leb_gemm_bf16_tc_sliced: %d slices leave one of them without a k-block (K %d)", n_slices, K);
+  LEB_REQUIRE(N % 4 == 0, "leb_gemm_bf16_tc_sliced: N (%d) must be a multiple of 4", N);
+  CUtensorMap ma, mw;
+  if (tensor_map(&ma, A, M, K, lda, TC_BM)) return 1;
+  if (tensor_map(&mw, W, N, K, K, 256)) return 1;
+  if (launch_tc<float, 256, 4>(part, ma, mw, M, N, K, N, 0, status, st, nullptr, n_slices)) return 1;
+  return leb_slices_finish(C, c_dtype, part, M, N, ldc, epilogue, n_slices, st);
 }
 
 // Grouped form for experts with many rows each (prompts): A [P, K] and C sorted by expert, rows

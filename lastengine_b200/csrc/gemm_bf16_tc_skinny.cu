@@ -326,6 +326,20 @@ skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, 
   }
 }
 
+int leb_slices_finish(void* C, int c_dtype, const float* part, int M, int N, int ldc, int epilogue, int n_slices,
+                      cudaStream_t st) {
+  const int cols = epilogue == 2 ? N / 2 : N;
+  dim3 grid(ceil_div(cols, 256), M);
+  if (c_dtype == LEB_F32)
+    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, part, M, N, ldc, epilogue, n_slices, FinishNorm{}, FinishConv{});
+  else if (c_dtype == LEB_BF16)
+    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, part, M, N, ldc, epilogue, n_slices, FinishNorm{}, FinishConv{});
+  else
+    return leb_fail("leb_slices_finish: unknown C dtype %d", c_dtype);
+  LEB_CHECK_LAUNCH("leb_slices_finish");
+  return 0;
+}
+
 template <int MP, int SK_STAGES>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, float* part, void* C, int c_dtype, int M,
                          int N, int K, int ldc, int epilogue, int n_slices, int* status, FinishNorm nm, cudaStream_t st) {

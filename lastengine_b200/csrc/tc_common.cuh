@@ -162,3 +162,7 @@ static int tensor_map(CUtensorMap* out, const void* ptr, int rows, int cols, int
   return 0;
 }
 
+// Adds up the partial products part[n_slices][M][N] in slice order and applies the epilogue (0 store,
+// 1 add into float C, 2 SwiGLU) into C; defined with the sliced decode product, whose second kernel it is.
+int leb_slices_finish(void* C, int c_dtype, const float* part, int M, int N, int ldc, int epilogue, int n_slices,
+                      cudaStream_t st);

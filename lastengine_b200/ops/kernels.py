@@ -133,6 +133,8 @@ def _declare(L) -> None:
         "leb_gemm_bf16_tc_supported": [P, P, I, I],
         "leb_gemm_bf16_tc": [P, I, P, P, I, I, I, I, I, I, P, P],
         "leb_selftest_bounded_wait": [P, I, I, P],
+        "leb_gemm_bf16_tc_slices": [I, I, I],
+        "leb_gemm_bf16_tc_sliced": [P, I, P, P, I, I, I, I, I, I, P, I, P, P],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -842,6 +844,13 @@ def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int
     N = w.shape[0]
     if not _tma_ok(x, w, K):
         return False
+    slices = L.leb_gemm_bf16_tc_slices(M, N, K) if N % 4 == 0 else 1
+    if slices > 1:      # a few hundred rows and a long K: fewer tiles than SMs, so K is cut as well
+        part = _skinny_workspace(x.device, slices * M * N)
+        _check(L.leb_gemm_bf16_tc_sliced(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
+                                         out.stride(0), epilogue, _ptr(part), slices,
+                                         _ptr(_status_word(x.device)), _stream()))
+        return True
     _check(L.leb_gemm_bf16_tc(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                               out.stride(0), epilogue, _ptr(_status_word(x.device)), _stream()))
     return True

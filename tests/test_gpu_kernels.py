@@ -760,6 +760,37 @@ def test_linear_tc(M, N, K_):
     assert err(base, b0.cpu().double() + want) < 2e-5
 
 
+@pytest.mark.parametrize("M,N,K_", [(300, 2048, 4096), (512, 2048, 5632), (200, 3072, 8192), (130, 264, 6080), (257, 1000, 4104)])
+def test_linear_tc_with_k_in_slices(M, N, K_):
+    """Products of a few hundred rows with a long K (prompts of that length, the down projection):
+    fewer 128 x 256 tiles than SMs, so K is cut into slices whose partial tiles a second kernel adds
+    up.  Store, add to the residual and SwiGLU against float64; a last slice with fewer k-blocks,
+    rows and columns past the tiles."""
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    assert K().lib().leb_gemm_bf16_tc_slices(M, N, K_) > 1
+    x, w = gen(M, K_, seed=110, dtype=torch.bfloat16), gen(N, K_, seed=111, scale=0.05, dtype=torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    assert K().linear_tc(out, x.to(DEV), w.to(DEV))
+    assert err(out, want) < 2e-5
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().linear_tc(ob, x.to(DEV), w.to(DEV))
+    assert err(ob, want) < 5e-3
+    base = gen(M, N, seed=112).to(DEV)
+    b0 = base.clone()
+    K().linear_tc(base, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert err(base, b0.cpu().double() + want) < 2e-5
+    again = b0.clone()
+    K().linear_tc(again, x.to(DEV), w.to(DEV), K().ACCUMULATE)
+    assert torch.equal(again, base)                  # the slices are added in a fixed order
+    if N % 32 == 0:
+        F = N // 2
+        o2 = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+        K().linear_tc(o2, x.to(DEV), fuse_gate_up(w[:F], w[F:], True).to(DEV), K().SWIGLU)
+        assert err(o2, P.silu(want[:, :F]) * want[:, F:]) < 6e-3
+    K().check_device_status()
+
+
 @pytest.mark.parametrize("M,F,D", [(128, 64, 64), (70, 16, 40), (300, 160, 96), (2048, 5632, 2048), (40, 5632, 128), (64, 1024, 64)])
 def test_linear_tc_swiglu_epilogue(M, F, D):
     from lastengine_b200.parts.ffn import fuse_gate_up
