@@ -2,6 +2,7 @@
 of cutting the work: each request alone and whole; with its last 32 tokens one by one; in
 batches of unequal lengths whose shorter requests end earlier, one batch after another so
 that slots and pages are used again; long decoding; the first tokens of a sequence."""
+import numpy as np
 import pytest
 import torch
 
@@ -92,6 +93,34 @@ def test_unequal_batches_reuse_slots(name, dtype, bf16, tol, model_dirs, engines
             check(g, plain(name, model_dirs, r, bf16), tol, f"{name} {dtype} batch from {lo}, len {len(r)}")
         eng.cache.check()
         assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("name", ["A", "D"])
+@pytest.mark.parametrize("dtype,bf16,tol", DTYPES)
+def test_batch_of_200_requests(name, dtype, bf16, tol, model_dirs):
+    """More sequences in a step than the decode products for up to 128 rows take: the prompts are one
+    step of some 1,500 rows, the decode steps have 200, then fewer and fewer rows (requests end at
+    different steps), so the products pass from the tiled kernels to the sliced and the streaming ones.
+    Then the same requests through generate(), captured steps (a bucket of 256) against plain ones."""
+    from lastengine_b200 import Engine, SamplingParams
+    cfg = CONFIGS[name][0]
+    rng = np.random.default_rng(21)
+    lengths = rng.integers(4, 22, size=200).tolist()
+    reqs = H.requests_for(cfg, lengths, 22)
+    prompt_lens = [max(1, n - int(d)) for n, d in zip(lengths, rng.integers(1, 13, size=200))]
+    eng = Engine.from_pretrained(model_dirs[name], dtype=dtype, max_tokens=200 * 64 + 1024)
+    got = H.run_batch(eng, reqs, prompt_lens)
+    for i in range(0, 200, 7):
+        check(got[i], plain(name, model_dirs, reqs[i], bf16), tol, f"{name} {dtype} request {i} of 200, len {lengths[i]}")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+    prompts = [r[:p] for r, p in zip(reqs, prompt_lens)]
+    sp = SamplingParams(temperature=0.0)
+    a = eng.generate(prompts, sp, max_new_tokens=6, max_batch=200, use_graphs=True)
+    b = eng.generate(prompts, sp, max_new_tokens=6, max_batch=200, use_graphs=False)
+    same = sum(x == y for x, y in zip(a.tokens, b.tokens))
+    assert same >= (200 if not bf16 else 190), f"{same} of 200 requests agree between captured and plain steps"
+    assert eng.cache.slots.n_held == 0
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
