@@ -65,7 +65,11 @@ def lfm3_plan(cfg: Lfm3Config) -> ModelPlan:
         layers=layers, schedule=[ScheduleEntry(i) for i in range(len(layers))],
         eos_token_ids=cfg.eos_token_ids,
         names={"embedding": "embed_tokens", "final_norm": "embedding_norm", "head": "lm_head"},
-        tensor_aliases=_alias)
+        tensor_aliases=_alias,
+        # the rotary frequency factors belong to the layers without a window; a model without such a
+        # layer may still carry them (the reference reads them if present and uses them there only,
+        # src/dense.rs:125)
+        unused_tensors=("rope_freqs.weight",))
 
 
 @ARCHITECTURES.register(*NAMES)

@@ -124,6 +124,8 @@ class ModelPlan:
     eos_token_ids: tuple[int, ...] = ()
     names: dict[str, str] = field(default_factory=dict)   # prefixes of embedding / final_norm / head
     tensor_aliases: Any = None     # callable: checkpoint name -> canonical name (or None)
+    unused_tensors: tuple[str, ...] = ()   # canonical names a checkpoint of the architecture may hold that this
+                                           # model has no use for (an optional tensor of a part no layer has): skipped
 
     def __post_init__(self):
         n = len(self.layers)

@@ -52,7 +52,8 @@ def load_model_dir(model, model_dir: str) -> None:
     for name, ref in ckpt.items():
         by_canonical[alias(name)] = ref
     specs = model.tensor_specs()
-    check_names(specs, {n: f.shape(k) for n, (f, k) in by_canonical.items()}, model_dir)
+    check_names(specs, {n: f.shape(k) for n, (f, k) in by_canonical.items()
+                        if n in specs or n not in plan.unused_tensors}, model_dir)
     tensors: dict[str, torch.Tensor] = {}
     for name, spec in specs.items():
         if name not in by_canonical:

@@ -138,6 +138,11 @@ def test_optional_tensors_frequency_factors_and_conv_bias(tmp_path):
     # only layers without a window take the factors (src/dense.rs:125)
     plan = plan_from_config(TINY_D)
     assert [l.mixer.params["position"].params["freq_factors"] for l in plan.layers if l.mixer.kind == "attention"] == [True, False]
+    # a model whose attention layers all have a window names no such tensor; its plan says that a
+    # checkpoint may carry it all the same (the loader then skips it instead of calling it unexpected)
+    only_windows = dict(TINY_D, layer_types=["conv", "sliding_attention", "sliding_attention", "conv"])
+    assert "rope_freqs.weight" not in specs_of(only_windows)
+    assert "rope_freqs.weight" in plan_from_config(only_windows).unused_tensors
     # a written folder leaves the optional tensor out; the test helper adds it
     d = H.make_model_dir(TINY_D, 3, str(tmp_path / "d"), freq_factors=True)
     ck = open_checkpoint(d)
