@@ -36,15 +36,19 @@ class DecodeGraph:
     that feed themselves) the move to the next position."""
 
     def __init__(self, engine, sampler: Sampler, bucket: int, table_width: int, self_feeding: bool = False,
-                 out: torch.Tensor | None = None, fed: bool = False, history=None, workspace: Workspace | None = None):
+                 out: torch.Tensor | None = None, fed: bool = False, history=None, workspace: Workspace | None = None,
+                 rows: int | None = None):
         """`table_width`: pages per sequence the step's page tables have; the longest sequence a
         replay can serve, and the length the split of the decode attention is chosen for.  `out`:
         where the chosen tokens go (shared between the graphs of one backend, so that a step of
         one bucket can take its tokens from the step of another).  `fed`: the step begins by
         taking tokens from `out` where the staged step says so.  `history`: (ring of recent
         tokens per cache slot [slots, 256], tokens seen per slot) on the device, for the penalties.
-        `workspace`: scratch shared with the other widths of the same bucket."""
+        `workspace`: scratch shared with the other widths of the same bucket.  `rows`: the step is
+        one of short prompts, padded to this many rows (`stage_prompts`); `bucket` then counts its
+        sequences with the padding ones."""
         self.history = history
+        self.rows = rows
         self.engine, self.sampler, self.bucket, self.width = engine, sampler, bucket, table_width
         self.self_feeding, self.fed = self_feeding, fed
         self.ws = workspace if workspace is not None else Workspace(engine.device)
@@ -98,6 +102,35 @@ class DecodeGraph:
         batch.max_kvlen = self.width * eng.cache.page_size
         self.batch = batch
         self.staged_slots = list(slots)
+        return grow
+
+    def stage_prompts(self, slots: list[int], prompts: list[list[int]], u01) -> dict[int, int]:
+        """Lays a step of whole prompts out in the fixed buffers: the prompts' rows, one row for each
+        padding sequence that fills the bucket, and a last padding sequence whose rows fill the
+        step up to `rows`.  What the captured kernels take as numbers (rows, sequences, the longest
+        prompt, the longest sequence) is the bucket's, not this step's."""
+        eng = self.engine
+        n = len(slots)
+        fill = self.bucket - 1 - n                       # padding sequences of one row
+        rest = self.rows - sum(len(p) for p in prompts) - fill
+        assert fill >= 0 and rest >= 1, "the bucket was chosen too small for the prompts"
+        seqs = list(slots) + [-1] * (fill + 1)
+        toks = [list(p) for p in prompts] + [[0]] * fill + [[0] * rest]
+        u = None
+        if self.sampler.needs_uniform():
+            u = np.zeros(self.bucket, dtype=np.float32)
+            u[:n] = u01
+        batch, grow = eng.prepare(seqs, toks, "last", u01=u, builder=self.builder, table_width=self.width)
+        if self.batch is not None:
+            same = (batch.tokens.data_ptr() == self.batch.tokens.data_ptr()
+                    and all(batch.tables[k].data_ptr() == self.batch.tables[k].data_ptr() for k in batch.tables))
+            if not same:
+                self.graph = None      # the staging buffer moved: capture again
+        assert batch.n_rows == self.rows and batch.n_seqs == self.bucket
+        batch.max_kvlen = self.width * eng.cache.page_size
+        batch.max_qlen = self.rows
+        self.batch = batch
+        self.staged_slots = []         # not a step restage() can follow
         return grow
 
     def restage(self, slots: list[int], tokens: list[int] | None, u01, feed=None) -> dict[int, int] | None:
@@ -310,9 +343,55 @@ class GraphBackend(EngineBackend):
         self._held = []
         self.engine.release([s for s in slots if self.engine.cache.slots.holds(s)])
 
+    # Short prompts as captured steps: a prompt step launches some 125 kernels from the host, which
+    # takes longer than the device needs for them below a few hundred rows.  Buckets of rows and of
+    # sequences; a step that fits none, or sampling with penalties (whose first token looks at the
+    # prompt on the host), runs uncaptured.
+    PROMPT_ROWS = (32, 64, 128, 256, 512)
+    PROMPT_SEQS = (1, 2, 4, 8)
+
+    def _start_captured(self, prompts, u01):
+        eng = self.engine
+        n = len(prompts)
+        if self.sampler.params.has_penalties or n > self.PROMPT_SEQS[-1] or any(len(p) == 0 for p in prompts):
+            return None
+        nb = next(b for b in self.PROMPT_SEQS if n <= b)
+        need = sum(len(p) for p in prompts) + (nb - n) + 1
+        rows = next((r for r in self.PROMPT_ROWS if need <= r), None)
+        if rows is None:
+            return None
+        page = eng.cache.page_size
+        width = 1
+        while width * page < max(len(p) for p in prompts) + 1:
+            width *= 2
+        if width > self.max_width:
+            return None
+        slots = [eng.new_sequence() for _ in prompts]
+        try:
+            out = self._chosen(nb + 1)
+            key = ("prompts", rows, nb, width)
+            g = self.graphs.get(key)
+            if g is None:
+                ws = self.graphs.setdefault(("prompt scratch", rows), Workspace(eng.device))
+                g = self.graphs[key] = DecodeGraph(eng, self.sampler, nb + 1, width, out=out, workspace=ws, rows=rows)
+            grow = g.stage_prompts(slots, prompts, u01)
+            g.launch()
+            eng.cache.commit(grow)
+            host = self._hosts[0]
+            host[:n + 1].copy_(kernels.status_and_tokens(eng.device, n), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            vals = host[:n + 1].tolist()
+            kernels.raise_on_status(vals[0], eng.device)
+            self.h2d_bytes = g.builder.last_h2d_bytes
+            return slots, vals[1:]
+        except Exception:
+            eng.release(slots)
+            raise
+
     def start(self, prompts, u01, histories):
         self._drain()
-        slots, toks = super().start(prompts, u01, histories)
+        captured = self._start_captured(prompts, u01)
+        slots, toks = captured if captured is not None else super().start(prompts, u01, histories)
         h = self._history()
         if h is not None:
             # the rings of the new sequences: their last tokens, the first chosen one among them

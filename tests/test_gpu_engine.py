@@ -183,6 +183,39 @@ def test_decode_graphs_follow_the_live_lengths_not_the_cache_size(dirs):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_run_as_captured_steps(dtype, dirs):
+    """Prompts of a few hundred tokens in all are a captured step too (buckets of rows and of
+    sequences, padded with sequences that hold no slot): the same tokens as the uncaptured path,
+    the buckets used again by later calls, longer prompts and sampling with penalties uncaptured."""
+    from lastengine_b200 import Engine, SamplingParams
+    eng = Engine.from_pretrained(dirs["A"], dtype=dtype, max_tokens=8192, max_seqs=16)
+    greedy = SamplingParams(temperature=0.0)
+    cases = [[5], [31], [3, 40, 17], [1, 1], [9, 2, 2, 7, 30, 1, 12, 25], [200], [300, 100, 60], [129, 64, 64, 1]]
+    agree = total = 0
+    for k, lens in enumerate(cases):
+        prompts = H.requests_for(TINY_A, lens, 70 + k)
+        a = eng.generate(prompts, greedy, max_new_tokens=5, stop_token_ids=[], use_graphs=True)
+        b = eng.generate(prompts, greedy, max_new_tokens=5, stop_token_ids=[], use_graphs=False)
+        agree += sum(x == y for x, y in zip(a.tokens, b.tokens))
+        total += len(lens)
+        assert eng.cache.slots.n_held == 0
+    assert agree == total if dtype == "float32" else agree >= total - 2, (agree, total)
+    keys = sorted(k[1:] for k in eng._decode_graphs[greedy] if isinstance(k, tuple) and k[0] == "prompts")
+    assert sorted({(r, b) for r, b, w in keys}) == [(32, 1), (32, 2), (64, 4), (128, 8), (256, 1), (512, 4)], keys
+    before = len(eng._decode_graphs[greedy])
+    eng.generate(H.requests_for(TINY_A, [20, 8], 90), greedy, max_new_tokens=3, stop_token_ids=[])
+    assert len(eng._decode_graphs[greedy]) == before            # (32, 2) again: nothing new is captured
+    eng.generate(H.requests_for(TINY_A, [400, 200], 91), greedy, max_new_tokens=3, stop_token_ids=[])
+    assert not any(isinstance(k, tuple) and k[0] == "prompts" and k[1] > 512 for k in eng._decode_graphs[greedy])
+    pen = SamplingParams(temperature=0.0, repeat_penalty=1.3)
+    x = eng.generate(H.requests_for(TINY_A, [20, 8], 92), pen, max_new_tokens=4, stop_token_ids=[], use_graphs=True)
+    y = eng.generate(H.requests_for(TINY_A, [20, 8], 92), pen, max_new_tokens=4, stop_token_ids=[], use_graphs=False)
+    assert x.tokens == y.tokens or dtype == "bfloat16"
+    assert not any(isinstance(k, tuple) and k[0] == "prompts" for k in eng._decode_graphs.get(pen, {}))
+    eng.cache.check()
+
+
 def test_split_norm_is_offered_only_where_the_reader_can_scale_its_rows():
     """A feed-forward so wide (gate and up together 38,016 rows) that the sliced product of 17-128
     rows does not take it: a decode step of 32 sequences must then run that layer's norm as a
