@@ -32,7 +32,7 @@ struct FinishNorm {
 
 // With four stages of up to 24 KB two blocks fit an SM, and must: the next product's blocks then start,
 // and fetch their first weights, under this one's (hence the register bound).
-template <int MP, int SK_STAGES>  // activation rows padded to 16..128 (the MMA's N); stages of the ring
+template <int MP, int SK_STAGES>  // activation rows padded to 16, 32, 64, 96 or 128 (the MMA's N); stages of the ring
 __global__ void __launch_bounds__(SK_THREADS, SK_STAGES <= 4 ? 2 : 1)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       float* __restrict__ part, void* __restrict__ C, int c_dtype, int M, int N, int K, int ldc,
@@ -384,7 +384,7 @@ LEB_API int leb_gemm_bf16_skinny_supported(const void* A, const void* W, int M, 
 static int skinny_product(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
                           int ldc, int epilogue, float* part, int n_slices, FinishNorm nm, FinishConv cv, int* status,
                           cudaStream_t st) {
-  const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 96 ? 96 : 128)));
   CUtensorMap mw, mx;
   if (tensor_map(&mw, W, N, K, K, 128)) return 1;
   if (tensor_map(&mx, A, M, K, lda, MP)) return 1;
@@ -395,11 +395,15 @@ static int skinny_product(void* C, int c_dtype, const void* A, const void* W, in
   // against 16.4), no faster inside a decode step, where the next product can then not start early.
 
   const int first_ep = epilogue == 3 ? 0 : epilogue;   // the convolution is the second kernel's
+  // From 65 rows on a stage has 28 or 32 KB: three of them, so that two blocks still fit an SM
+  // (measured at batch 96 and 128: 1.26 and 1.47 ms a decode step, against 1.35 and 1.56 with four
+  // stages and 1.38 and 1.55 with six stages of the 128-row form alone).
   switch (MP) {
     case 16: rc = launch_skinny<16, 4>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
     case 32: rc = launch_skinny<32, 4>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
     case 64: rc = launch_skinny<64, 4>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
-    default: rc = launch_skinny<128, 6>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
+    case 96: rc = launch_skinny<96, 3>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
+    default: rc = launch_skinny<128, 3>(mw, mx, part, C, c_dtype, M, N, K, ldc, first_ep, n_slices, status, nm, st); break;
   }
   if (rc || n_slices == 1) return rc;
   const int cols = epilogue == 2 ? N / 2 : (epilogue == 3 ? N / 3 : N);

@@ -314,7 +314,7 @@ def test_shortconv_many_rows(Lc, D):
 
 
 @pytest.mark.parametrize("B,D,K_,Lc", [(8, 2048, 2048, 3), (1, 72, 40, 2), (13, 136, 200, 4), (16, 48, 64, 5), (5, 100, 72, 3),
-                                       (40, 2048, 2048, 3), (100, 136, 1024, 4), (18, 48, 512, 5)])
+                                       (40, 2048, 2048, 3), (100, 136, 1024, 4), (18, 48, 512, 5), (90, 136, 1024, 4)])
 def test_shortconv_decode_fused(B, D, K_, Lc):
     """Projection and convolution of a decode step without a convolution kernel (up to 16 sequences:
     one launch; more: the sliced product, whose second kernel convolves), three steps in a row so that the
@@ -363,7 +363,8 @@ def test_shortconv_decode_fused(B, D, K_, Lc):
 
 
 @pytest.mark.parametrize("M,D,K_,N2", [(8, 2048, 2048, 6144), (1, 72, 40, 64), (13, 136, 200, 96), (16, 104, 64, 32),
-                                       (64, 2048, 5632, 6144), (17, 72, 40, 64), (100, 136, 200, 96), (128, 104, 64, 32)])
+                                       (64, 2048, 5632, 6144), (17, 72, 40, 64), (100, 136, 200, 96), (128, 104, 64, 32),
+                                       (80, 2048, 5632, 6144), (96, 136, 200, 96)])
 def test_norm_split_between_two_products(M, D, K_, N2):
     """An RMSNorm split between the product that adds into the residual and the product that reads
     the normed rows (decode steps): the first leaves bfloat16(x * g) and partial sums of x^2, the
@@ -870,7 +871,8 @@ def test_linear_tc_pairs(M, N, K_):
 
 
 @pytest.mark.parametrize("M,N,K_", [(17, 2048, 2048), (64, 352, 128), (100, 6144, 64), (33, 11264, 192), (128, 100, 200),
-                                    (1, 128, 64), (16, 48, 72), (48, 2048, 5632), (64, 65536, 256)])
+                                    (1, 128, 64), (16, 48, 72), (48, 2048, 5632), (64, 65536, 256),
+                                    (65, 2048, 2048), (96, 352, 5632), (90, 100, 200), (97, 6144, 136)])
 def test_linear_skinny(M, N, K_):
     """The swapped-operand tcgen05 product with K sliced over blocks: store, add to residual, both
     result types, sizes that leave partial tiles and slices."""
@@ -890,7 +892,7 @@ def test_linear_skinny(M, N, K_):
     assert err(base, b0.cpu().double() + want) < 2e-5
 
 
-@pytest.mark.parametrize("M,F,D", [(64, 5632, 2048), (20, 16, 40), (100, 160, 96)])
+@pytest.mark.parametrize("M,F,D", [(64, 5632, 2048), (20, 16, 40), (100, 160, 96), (80, 5632, 2048), (96, 160, 96)])
 def test_linear_skinny_swiglu(M, F, D):
     from lastengine_b200.parts.ffn import fuse_gate_up
     x = gen(M, D, seed=123, dtype=torch.bfloat16)
