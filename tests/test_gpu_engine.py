@@ -208,6 +208,12 @@ def test_short_prompts_run_as_captured_steps(dtype, dirs):
     assert len(eng._decode_graphs[greedy]) == before            # (32, 2) again: nothing new is captured
     eng.generate(H.requests_for(TINY_A, [400, 200], 91), greedy, max_new_tokens=3, stop_token_ids=[])
     assert not any(isinstance(k, tuple) and k[0] == "prompts" and k[1] > 512 for k in eng._decode_graphs[greedy])
+    # sampling with a temperature: the uniform numbers reach the captured prompt step as they reach the plain one
+    warm = SamplingParams(temperature=0.8, top_k=20, seed=3)
+    u = eng.generate(H.requests_for(TINY_A, [20, 8, 33], 93), warm, max_new_tokens=6, stop_token_ids=[], use_graphs=True)
+    v = eng.generate(H.requests_for(TINY_A, [20, 8, 33], 93), warm, max_new_tokens=6, stop_token_ids=[], use_graphs=False)
+    assert u.tokens == v.tokens or dtype == "bfloat16"
+    assert any(isinstance(k, tuple) and k[0] == "prompts" for k in eng._decode_graphs[warm])
     pen = SamplingParams(temperature=0.0, repeat_penalty=1.3)
     x = eng.generate(H.requests_for(TINY_A, [20, 8], 92), pen, max_new_tokens=4, stop_token_ids=[], use_graphs=True)
     y = eng.generate(H.requests_for(TINY_A, [20, 8], 92), pen, max_new_tokens=4, stop_token_ids=[], use_graphs=False)
