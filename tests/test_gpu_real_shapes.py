@@ -176,6 +176,34 @@ def test_greedy_generation_of_64_requests_graphs_on_and_off(dtype, dense_dir, en
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_as_captured_steps_at_real_sizes(dtype, dense_dir, engines):
+    """Prompts of a few hundred rows in all through the entry point: with graphs they are one
+    captured step (a bucket of rows and sequences, padded), without them a plain step; the same
+    tokens, and where the two part ways the two best logits there are a near-tie."""
+    from lastengine_b200 import SamplingParams
+    eng = engines(dtype)
+    greedy = SamplingParams(temperature=0.0)
+    for lens in ([40, 100, 200], [7], [250, 3]):
+        prompts = H.requests_for(REAL_DENSE, lens, 56 + len(lens))
+        fast = eng.generate(prompts, greedy, max_new_tokens=8, stop_token_ids=[])
+        slow = eng.generate(prompts, greedy, max_new_tokens=8, stop_token_ids=[], use_graphs=False)
+        for i, (a, b) in enumerate(zip(fast.tokens, slow.tokens)):
+            if a == b:
+                continue
+            j = next(k for k in range(min(len(a), len(b)) + 1) if a[k:k + 1] != b[k:k + 1])
+            s = eng.new_sequence()
+            lg = eng.step([s], [prompts[i] + b[:j]], "last")[0].double()
+            eng.release(s)
+            top = torch.topk(lg, 2).values
+            gap = float((top[0] - top[1]) / lg.abs().max())
+            assert gap < (H.TOL_BF16 if dtype == "bfloat16" else H.TOL_F32), \
+                f"{dtype}: prompts {lens}, request {i} differs at token {j} with a clear best logit (gap {gap:.2e})"
+    assert any(isinstance(k, tuple) and k[0] == "prompts" for k in eng._decode_graphs[greedy])
+    status_clear()
+    assert eng.cache.slots.n_held == 0
+
+
 def test_expert_layers_of_real_size(moe_dir):
     """The 8B-A1B shape's expert layer (32 experts of 1792, 4 per token) in bfloat16: a prompt of
     700 tokens (the grouped tcgen05 product), its last 32 tokens one by one (the grouped weight
