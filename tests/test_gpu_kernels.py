@@ -697,6 +697,32 @@ def test_moe_router_align_combine(dtype, E, k, norm, bias, scaling):
     assert err(x, want) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,k,D", [(32, 4, 2048), (8, 2, 104), (5, 1, 72), (64, 6, 520)])
+def test_moe_router_gives_a_row_the_same_bits_whatever_the_step(dtype, E, k, D):
+    """The router has a form for single rows and one for four rows per block (many rows): a row's
+    experts and weights are the same bits in both, so that a token is routed the same way alone, in a
+    decode batch and inside a prompt."""
+    M = 700
+    h = gen(M, D, seed=97, dtype=dtype).to(DEV)
+    wr, b = gen(E, D, seed=98, scale=0.3).to(DEV), gen(E, seed=99, scale=0.1).to(DEV)
+    def route(rows):
+        ids = torch.empty(rows.shape[0], k, dtype=torch.int32, device=DEV)
+        wts = torch.empty(rows.shape[0], k, device=DEV)
+        K().moe_router(ids, wts, rows, wr, b, True, 1.5)
+        return ids, wts
+    all_ids, all_w = route(h)                                  # many rows: four per block
+    some_ids, some_w = route(h[:200].contiguous())
+    assert torch.equal(some_ids, all_ids[:200]) and torch.equal(some_w, all_w[:200])
+    for lo in (0, 199, 693):
+        one_ids, one_w = route(h[lo:lo + 7].contiguous())      # a row per block
+        assert torch.equal(one_ids, all_ids[lo:lo + 7]) and torch.equal(one_w, all_w[lo:lo + 7])
+    want_ids, want_w, _ = P.moe_route(h.double().cpu(), wr.double().cpu(), b.double().cpu(), k, True, 1.5)
+    agree = (all_ids.cpu().long() == want_ids).all(dim=1)
+    assert agree.float().mean() > 0.97                        # the rest: near-ties at float rounding
+    assert err(all_w[agree.to(DEV)], want_w[agree]) < 1e-5
+
+
 # ---- sampling ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("V", [256, 1000, 65536])
 def test_argmax_and_sampling(V):
