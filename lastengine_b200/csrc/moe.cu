@@ -352,7 +352,7 @@ LEB_API int leb_moe_align(int* offsets, int* sorted_pair, int* pair_row, const i
 // A thread owns VEC consecutive columns of one token; the token's k rows and weights are read
 // first and then all k pieces of ys are asked for before any is used, so the kernel costs two
 // trips to memory whatever k is.
-template <int VEC>
+template <int VEC, int KMAX>   // columns a thread owns; the most rows per token (k <= KMAX)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const int* __restrict__ pair_row,
                    const float* __restrict__ topk_w, int D, int k, int accumulate) {
@@ -361,10 +361,10 @@ moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const in
   const size_t m = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (i >= D) return;
-  int row[MOE_MAX_K];
-  float w[MOE_MAX_K], old[VEC], v[MOE_MAX_K][VEC];
+  int row[KMAX];
+  float w[KMAX], old[VEC], v[KMAX][VEC];
 #pragma unroll
-  for (int j = 0; j < MOE_MAX_K; j++) {
+  for (int j = 0; j < KMAX; j++) {
     row[j] = j < k ? pair_row[m * k + j] : 0;
     w[j] = j < k ? topk_w[m * k + j] : 0.f;
   }
@@ -376,11 +376,11 @@ moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const in
     old[0] = accumulate ? *o : 0.f;
   }
 #pragma unroll
-  for (int j = 0; j < MOE_MAX_K; j++) {
+  for (int j = 0; j < KMAX; j++) {
     if (j < k) {
       const float* p = ys + (size_t)row[j] * D + i;
       if (VEC == 4) {
-        const float4 t = *reinterpret_cast<const float4*>(p);
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(p));     // read once: no need to keep it in L2
         v[j][0] = t.x; v[j][1 % VEC] = t.y; v[j][2 % VEC] = t.z; v[j][3 % VEC] = t.w;
       } else {
         v[j][0] = *p;
@@ -391,7 +391,7 @@ moe_combine_kernel(float* __restrict__ x, const float* __restrict__ ys, const in
 #pragma unroll
   for (int e = 0; e < VEC; e++) a[e] = 0.f;
 #pragma unroll
-  for (int j = 0; j < MOE_MAX_K; j++)
+  for (int j = 0; j < KMAX; j++)
     if (j < k)
 #pragma unroll
       for (int e = 0; e < VEC; e++) a[e] += w[j] * v[j][e];
@@ -406,10 +406,13 @@ LEB_API int leb_moe_combine(float* x, const float* ys, const int* pair_row, cons
                             int M, int D, int k, int accumulate, cudaStream_t st) {
   if (M <= 0) return 0;
   LEB_REQUIRE(k >= 1 && k <= MOE_MAX_K, "leb_moe_combine: %d rows per token outside 1..%d", k, MOE_MAX_K);
-  if (D % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)ys & 15) == 0)
-    leb_launch(moe_combine_kernel<4>, dim3(M, ceil_div(D, 1024)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
-  else
-    leb_launch(moe_combine_kernel<1>, dim3(M, ceil_div(D, 256)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+  if (D % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)ys & 15) == 0) {
+    // up to four rows per token (the usual case) with arrays of four: fewer registers, more blocks per SM
+    if (k <= 4) leb_launch(moe_combine_kernel<4, 4>, dim3(M, ceil_div(D, 1024)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+    else leb_launch(moe_combine_kernel<4, MOE_MAX_K>, dim3(M, ceil_div(D, 1024)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+  } else {
+    leb_launch(moe_combine_kernel<1, MOE_MAX_K>, dim3(M, ceil_div(D, 256)), dim3(256), 0, st, x, ys, pair_row, topk_w, D, k, accumulate);
+  }
   LEB_CHECK_LAUNCH("leb_moe_combine");
   return 0;
 }
