@@ -76,16 +76,26 @@ moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const 
 #pragma unroll
     for (int r = 0; r < R; r++) z[r] = 0.f;
     if (VEC == 4) {
+      // eight pieces of the router row are asked for before the first is used: a loop that fetched
+      // a piece and used it spent a round trip to L2 on each (16 of them for a width of 2,048)
       const float4* w4 = reinterpret_cast<const float4*>(w);
-      for (int i = lane; i < D / 4; i += 32) {
-        const float4 a = w4[i];
+      const int n4 = D / 4;
+      for (int i0 = lane; i0 < n4; i0 += 32 * 8) {
+        float4 a[8];
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-          const float4 x = reinterpret_cast<const float4*>(hs + (size_t)r * D)[i];
-          z[r] += a.x * x.x;
-          z[r] += a.y * x.y;
-          z[r] += a.z * x.z;
-          z[r] += a.w * x.w;
+        for (int u = 0; u < 8; u++) a[u] = i0 + 32 * u < n4 ? w4[i0 + 32 * u] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const int i = i0 + 32 * u;
+          if (i >= n4) break;
+#pragma unroll
+          for (int r = 0; r < R; r++) {
+            const float4 x = reinterpret_cast<const float4*>(hs + (size_t)r * D)[i];
+            z[r] += a[u].x * x.x;
+            z[r] += a[u].y * x.y;
+            z[r] += a[u].z * x.z;
+            z[r] += a[u].w * x.w;
+          }
         }
       }
     } else {
