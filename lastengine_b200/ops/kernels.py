@@ -582,7 +582,10 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
     cores with float accumulation.  `epilogue`: STORE, ACCUMULATE (out is the float residual)
     or SWIGLU (w holds gate and up rows interleaved in blocks of 16; out has N/2 columns).
     Up to SMALL_M rows bfloat16 products stream W through shared memory with asynchronous copies;
-    with more rows they go to the tcgen05 kernels; `streaming` asks for the register-fed
+    with more rows they go to the tcgen05 kernels: up to SKINNY_M rows with W as the wide operand
+    and K cut into slices (a second kernel adds them up), above that 128 x BN tiles (K cut as well
+    where a few hundred rows and a long K leave most SMs without a tile), from PAIRS_MIN_ROWS rows
+    and large matrices 256 x 256 tiles on pairs of SMs; `streaming` asks for the register-fed
     weight-streaming kernel (the one that also serves grouped products) whatever the row count.
     """
     _cuda(x, "linear.x", contiguous=False)
